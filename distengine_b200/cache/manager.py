@@ -187,7 +187,9 @@ class CacheManager:
         for group in self.paged:
             shape = (len(group.entries), num_pages, group.spec.kv_heads, page_size)
             group.k = torch.zeros((*shape, group.spec.head_dim), dtype=dtype, device=self.device)
-            group.v = torch.zeros((*shape, group.spec.v_dim), dtype=dtype, device=self.device)
+            # values that are features of the key rows have no pages of their own
+            group.v = (group.k if group.spec.values_in_keys else
+                       torch.zeros((*shape, group.spec.v_dim), dtype=dtype, device=self.device))
             if self.poison:
                 group.k.fill_(float("nan"))
                 group.v.fill_(float("nan"))
@@ -211,7 +213,8 @@ class CacheManager:
             for spec in (entry if isinstance(entry, tuple) else (entry,)):
                 if isinstance(spec, PagedKVSpec):
                     groups[spec] = groups.get(spec, 0) + 1
-        return sum(layers * spec.kv_heads * page_size * (spec.head_dim + spec.v_dim) * size
+        return sum(layers * spec.kv_heads * page_size * size
+                   * (spec.head_dim + (0 if spec.values_in_keys else spec.v_dim))
                    for spec, layers in groups.items())
 
     @property

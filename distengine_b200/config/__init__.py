@@ -1,7 +1,8 @@
 from .engine import EngineConfig, parse_dtype
 from .llama import LlamaConfig
+from .vapelix import VapelixConfig
 from .vomotar import VomotarConfig
 from .model import ConfigError, LayerSpec, ModelConfig, PartSpec, PlanEntry
 
-__all__ = ["EngineConfig", "parse_dtype", "LlamaConfig", "VomotarConfig", "ConfigError", "LayerSpec",
+__all__ = ["EngineConfig", "parse_dtype", "LlamaConfig", "VomotarConfig", "VapelixConfig", "ConfigError", "LayerSpec",
            "ModelConfig", "PartSpec", "PlanEntry"]

@@ -9,7 +9,8 @@ A model is described as data:
   prefixes under which its tensors are stored.  Layers of one model may differ.
 * ``PlanEntry`` - one execution of a layer.  The plan is the order in which layers run; it may name
   a layer twice (each run that writes has a cache of its own) or let a run read the cache that an
-  earlier run wrote (``reads_cache_of``), in which case it writes nothing.
+  earlier run wrote (``reads_cache_of``), in which case it writes nothing.  An entry with
+  ``adds_embedding`` starts a new pass over looped layers: the embedding rows join the stream again.
 
 The reference builds one fixed stack (src/models/llama.py:112-124) and loops over it
 (:183-189); it has no layer specs and no plan.
@@ -53,6 +54,9 @@ class LayerSpec:
     prefixes: tuple[tuple[str, str], ...] = ()
     # the norm before the feed-forward, where it is not the same as ``norm`` (another tensor name)
     feed_forward_norm: "PartSpec | None" = None
+    # what is added to the stream after the layer's branches from the token itself (a kind of the
+    # side-input registry), or None; its tensors live under the prefix of role "side_input"
+    side_input: "PartSpec | None" = None
 
     def prefix(self, role: str) -> str:
         return dict(self.prefixes)[role]
@@ -62,6 +66,9 @@ class LayerSpec:
 class PlanEntry:
     layer: int
     reads_cache_of: int | None = None     # index of an earlier plan entry
+    # the embedding rows (the stream as it was before the first entry) are added to the stream
+    # before this entry runs
+    adds_embedding: bool = False
 
 
 @dataclass(frozen=True)

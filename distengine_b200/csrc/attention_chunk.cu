@@ -44,6 +44,8 @@ struct Sight {
     int window;         // > 0: the last `window` keys only ...
     int keep_first;     // ... and the first `keep_first` keys of the sequence
     float softcap;      // > 0: score <- softcap * tanh(score / softcap)
+    int v_stride;       // elements from one key's values to the next in v_pages: dv, or the key
+                        // size where the values are the first dv features of the key rows
 };
 
 // first key of the near range of a row at `pos` (does not fall as pos grows)
@@ -310,7 +312,7 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out,
             for (int i = lane; i < dk; i += 32)
                 Ks[j * (dk + 1) + i] = read ? to_float(k_pages[at * dk + i]) : 0.0f;
             for (int i = lane; i < dv; i += 32)
-                Vs[j * dv + i] = read ? to_float(v_pages[at * dv + i]) : 0.0f;
+                Vs[j * dv + i] = read ? to_float(v_pages[at * sight.v_stride + i]) : 0.0f;
             if (lane == 0) {
                 Ks[j * (dk + 1) + dk] = held ? 0.0f : -INFINITY;
                 if (!held && status != nullptr) atomicExch(status, 2);
@@ -463,7 +465,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ 
                 continue;
             }
             const size_t at = ((size_t)page_id * kv_heads + hk) * page + (size_t)(kpos % page);
-            const T* src = w < ck ? k_pages + at * dk + w * PN : v_pages + at * dv + (w - ck) * PN;
+            const T* src = w < ck ? k_pages + at * dk + w * PN : v_pages + at * sight.v_stride + (w - ck) * PN;
             pre[c] = *reinterpret_cast<const uint4*>(src);
         }
     };
@@ -707,7 +709,7 @@ attn_chunk_tiled_kernel(const T* __restrict__ q, int q_stride, void* __restrict_
             }
             const bool read = inside && !gone;
             const T* ksrc = k_pages + at * dk;
-            const T* vsrc = v_pages + at * dv;
+            const T* vsrc = v_pages + at * sight.v_stride;
             float* kdst = Ks + j * kst;
             float* vdst = Vs + j * dv;
             for (int w = w0; w < per_key; w += 16) {
@@ -1020,7 +1022,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
                 const bool ok = __shfl_sync(0xffffffffu, (int)valid, j) != 0;
                 if (ok)
                     cp_async_16(mine + TILE * k_stride + ((size_t)j * dv + w * PN) * sizeof(T),
-                                v_pages + (size_t)rj * dv + w * PN);
+                                v_pages + (size_t)rj * sight.v_stride + w * PN);
             }
             asm volatile("cp.async.commit_group;\n" ::: "memory");
             asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -1205,9 +1207,12 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
                                    int page, float scale, int chunk, int window, int keep_first,
                                    float softcap, int out_f32, int fused, const float* fk, int rot,
                                    const float* fv, int write_kv, const void* gate, int ld_gate,
-                                   int* status, void* stream) {
+                                   int v_stride, int* status, void* stream) {
     if (n_seqs <= 0) return 0;
-    const Sight sight = {chunk, window, keep_first, softcap};
+    // v_stride 0: values in rows of their own; else rows of v_pages are that many elements apart
+    const int pn_v = dtype == DE_BF16 ? 8 : 4;
+    if (v_stride != 0 && (v_stride < dv || v_stride % pn_v != 0 || fused)) return -2;
+    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv};
     const Fuse fuse = {fused, fk, rot, fv, write_kv, gate, ld_gate};
     if (fused && (rot < 0 || rot % 2 || rot > dk || (fv != nullptr && dv % 2) || out_f32)) return -2;
     if (!de_attn_chunk_decode_ok(dtype, heads, kv_heads, dk, dv) || (uintptr_t)k_pages % 16 != 0)
@@ -1306,9 +1311,12 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
                             const int* items, int num_items, const float* r1, const float* r2,
                             int heads, int kv_heads, int dk, int dv, int page, float scale,
                             int chunk, int window, int keep_first, float softcap, int out_f32,
-                            int tile_rows, int* status, void* stream) {
+                            int tile_rows, int v_stride, int* status, void* stream) {
     if (num_items <= 0) return 0;
-    const Sight sight = {chunk, window, keep_first, softcap};
+    // v_stride 0: values in rows of their own; else rows of v_pages are that many elements apart
+    if (v_stride != 0 && (v_stride < dv || (vec_ok(dtype, dk, dv) && v_stride % (dtype == DE_BF16 ? 8 : 4))))
+        return -2;
+    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv};
     if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     if (tile_rows != ROWS && !((tile_rows == ROWS * 4 || tile_rows == TROWS) && vec_ok(dtype, dk, dv)))

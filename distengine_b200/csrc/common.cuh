@@ -54,7 +54,7 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* 33 floats 
 }
 
 // Activations by number (the C interface's `kind`): 0 the square of relu, 1 tanh, 2 silu,
-// 3 gelu in its tanh form.
+// 3 gelu in its tanh form, 4 gelu in its exact form (with the error function).
 __device__ __forceinline__ float de_activate(float x, int kind) {
     if (kind == 0) {
         const float r = fmaxf(x, 0.0f);
@@ -62,6 +62,7 @@ __device__ __forceinline__ float de_activate(float x, int kind) {
     }
     if (kind == 1) return tanhf(x);
     if (kind == 2) return x / (1.0f + expf(-x));
+    if (kind == 4) return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
     return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 

@@ -777,6 +777,7 @@ DE_EXPORT int de_add_layernorm(int dtype, int weight_dtype, float* resid, const 
 // ------------------------------------------------------------------------------------------
 // An activation over a block of columns of a matrix, float32 arithmetic:
 //   kind 0: relu(x)^2     kind 1: tanh(x)     kind 2: silu(x)     kind 3: gelu (tanh form)
+//   kind 4: gelu (exact form)
 // x [n, cols] with row stride ldx, out [n, cols] with row stride ldo (out may be x).
 // ------------------------------------------------------------------------------------------
 template <typename T>
@@ -813,7 +814,7 @@ __global__ void activation_vec_kernel(const T* __restrict__ x, int ldx, T* __res
 DE_EXPORT int de_activation(int dtype, const void* x, int ldx, void* out, int ldo, int n, int cols,
                             int kind, void* stream) {
     if (n <= 0 || cols <= 0) return 0;
-    if (kind < 0 || kind > 3) return -2;
+    if (kind < 0 || kind > 4) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
     const int piece = dtype == DE_BF16 ? 8 : 16;
@@ -877,4 +878,196 @@ DE_EXPORT int de_scaled_sum(int dtype, const float* a, const float* b, float sa,
                          a, b, sa, sb, (__nv_bfloat16*)out, (size_t)total);
     return de_launch(scaled_sum_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, a, b, sa,
                      sb, (float*)out, (size_t)total);
+}
+
+// ------------------------------------------------------------------------------------------
+// The residual sum of a layer whose branches read the same input: resid += (a + b) + extra, every
+// sum in float32; a and b are branch outputs of their own types (either may be null), extra is
+// float32 (the embedding rows that join the stream again before a further pass; may be null).
+// rows (optional) receives the new residual in the activation type, for a product that reads it.
+// ------------------------------------------------------------------------------------------
+template <typename A, typename B, typename T>
+__global__ void residual_add_kernel(float* __restrict__ resid, const A* __restrict__ a,
+                                    const B* __restrict__ b, const float* __restrict__ extra,
+                                    T* __restrict__ rows, size_t total) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        float x = resid[idx];
+        if (a != nullptr && b != nullptr) x += to_float(a[idx]) + to_float(b[idx]);
+        else if (a != nullptr) x += to_float(a[idx]);
+        else if (b != nullptr) x += to_float(b[idx]);
+        if (extra != nullptr) x += extra[idx];
+        resid[idx] = x;
+        if (rows != nullptr) rows[idx] = from_float<T>(x);
+    }
+}
+
+DE_EXPORT int de_residual_add(float* resid, int a_dtype, const void* a, int b_dtype, const void* b,
+                              const float* extra, int rows_dtype, void* rows, long long total,
+                              void* stream) {
+    if (total <= 0) return 0;
+    size_t blocks = ((size_t)total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    cudaStream_t s = (cudaStream_t)stream;
+#define RADD(A, B, T)                                                                           \
+    return de_launch(residual_add_kernel<A, B, T>, dim3((unsigned)blocks), dim3(256), 0, s,     \
+                     resid, (const A*)a, (const B*)b, extra, (T*)rows, (size_t)total)
+#define RADD_T(A, B)                                                                            \
+    do {                                                                                        \
+        if (rows_dtype == DE_BF16) RADD(A, B, __nv_bfloat16);                                   \
+        RADD(A, B, float);                                                                      \
+    } while (0)
+    if (a_dtype == DE_BF16 && b_dtype == DE_BF16) RADD_T(__nv_bfloat16, __nv_bfloat16);
+    if (a_dtype == DE_BF16) RADD_T(__nv_bfloat16, float);
+    if (b_dtype == DE_BF16) RADD_T(float, __nv_bfloat16);
+    RADD_T(float, float);
+#undef RADD_T
+#undef RADD
+}
+
+// out[n, i] = act(x[n, i]) * x[n, inner + i]: the gate of a gated feed-forward with any of the
+// activations.  x [n, 2 inner] with row stride ldx, out [n, inner] with row stride ldo.
+template <typename T>
+__global__ void act_mul_kernel(const T* __restrict__ x, int ldx, T* __restrict__ out, int ldo,
+                               int inner, size_t total, int kind) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / inner;
+        const int i = (int)(idx - n * inner);
+        const float g = de_activate(to_float(x[n * ldx + i]), kind);
+        out[n * ldo + i] = from_float<T>(g * to_float(x[n * ldx + inner + i]));
+    }
+}
+
+DE_EXPORT int de_act_mul(int dtype, const void* x, int ldx, void* out, int ldo, int n, int inner,
+                         int kind, void* stream) {
+    if (n <= 0 || inner <= 0) return 0;
+    if (kind < 0 || kind > 4) return -2;
+    const size_t total = (size_t)n * inner;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(act_mul_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
+                         (const __nv_bfloat16*)x, ldx, (__nv_bfloat16*)out, ldo, inner, total, kind);
+    return de_launch(act_mul_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s,
+                     (const float*)x, ldx, (float*)out, ldo, inner, total, kind);
+}
+
+// out[n, i] = act(z[n, i]) * table[ids[n], i]: a small projection of the stream gated by a row of a
+// table that the token picks.  z, out [n, dim] (row strides ldz, ldo), table [vocab, dim].
+template <typename T>
+__global__ void act_mul_row_kernel(const T* __restrict__ z, int ldz, const int* __restrict__ ids,
+                                   const T* __restrict__ table, int vocab, T* __restrict__ out,
+                                   int ldo, int dim, size_t total, int kind) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / dim;
+        const int i = (int)(idx - n * dim);
+        const int id = ids[n];
+        const float e = (id >= 0 && id < vocab) ? to_float(table[(size_t)id * dim + i]) : 0.0f;
+        out[n * ldo + i] = from_float<T>(de_activate(to_float(z[n * ldz + i]), kind) * e);
+    }
+}
+
+DE_EXPORT int de_act_mul_row(int dtype, const void* z, int ldz, const int* ids, const void* table,
+                             int vocab, void* out, int ldo, int n, int dim, int kind,
+                             void* stream) {
+    if (n <= 0 || dim <= 0) return 0;
+    if (kind < 0 || kind > 4) return -2;
+    const size_t total = (size_t)n * dim;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(act_mul_row_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
+                         (const __nv_bfloat16*)z, ldz, ids, (const __nv_bfloat16*)table, vocab,
+                         (__nv_bfloat16*)out, ldo, dim, total, kind);
+    return de_launch(act_mul_row_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s,
+                     (const float*)z, ldz, ids, (const float*)table, vocab, (float*)out, ldo, dim,
+                     total, kind);
+}
+
+// resid[n] += y[n] / sqrt(mean(y[n]^2) + eps) * weight, all in float32 (a normed branch that joins
+// the stream unrounded).  y [n, width] of the activation type, one block a row.
+template <typename T, typename W>
+__global__ void add_normed_kernel(float* __restrict__ resid, const T* __restrict__ y,
+                                  const W* __restrict__ weight, int width, float eps) {
+    __shared__ float scratch[33];
+    const size_t row = blockIdx.x;
+    const T* yr = y + row * width;
+    pdl_wait();
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = to_float(yr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)width + eps);
+    pdl_trigger();
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        resid[row * width + i] += to_float(yr[i]) * inv * to_float(weight[i]);
+}
+
+DE_EXPORT int de_add_normed(int dtype, int weight_dtype, float* resid, const void* y,
+                            const void* weight, int n, int width, float eps, void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+#define ADDN(T, W)                                                                              \
+    return de_launch(add_normed_kernel<T, W>, dim3(n), dim3(threads), 0, s, resid, (const T*)y,  \
+                     (const W*)weight, width, eps)
+    if (dtype == DE_BF16) {
+        if (weight_dtype == DE_BF16) ADDN(__nv_bfloat16, __nv_bfloat16);
+        ADDN(__nv_bfloat16, float);
+    }
+    if (weight_dtype == DE_BF16) ADDN(float, __nv_bfloat16);
+    ADDN(float, float);
+#undef ADDN
+}
+
+// out[n, i] = x[n, col0 + i] / sqrt(mean over the cols of x^2 + eps) * weight[i]: an RMS norm over a
+// block of columns of a product's output (a latent between two products).  Rounded to the
+// activation type before and after the weight, as the stream's norm is.  One block a row.
+template <typename T, typename W>
+__global__ void rmsnorm_cols_kernel(const T* __restrict__ x, int ldx, const W* __restrict__ weight,
+                                    T* __restrict__ out, int ldo, int cols, float eps) {
+    __shared__ float scratch[33];
+    const size_t row = blockIdx.x;
+    const T* xr = x + row * ldx;
+    pdl_wait();
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = to_float(xr[i]);
+        ss = fmaf(v, v, ss);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(ss, scratch) / (float)cols + eps);
+    pdl_trigger();
+    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+        const float v = to_float(from_float<T>(to_float(xr[i]) * inv));
+        out[row * ldo + i] = from_float<T>(v * to_float(weight[i]));
+    }
+}
+
+DE_EXPORT int de_rmsnorm_cols(int dtype, int weight_dtype, const void* x, int ldx,
+                              const void* weight, void* out, int ldo, int n, int cols, float eps,
+                              void* stream) {
+    if (n <= 0 || cols <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = cols >= 2048 ? 512 : (cols >= 512 ? 256 : 128);
+#define NORMC(T, W)                                                                             \
+    return de_launch(rmsnorm_cols_kernel<T, W>, dim3(n), dim3(threads), 0, s, (const T*)x, ldx,  \
+                     (const W*)weight, (T*)out, ldo, cols, eps)
+    if (dtype == DE_BF16) {
+        if (weight_dtype == DE_BF16) NORMC(__nv_bfloat16, __nv_bfloat16);
+        NORMC(__nv_bfloat16, float);
+    }
+    if (weight_dtype == DE_BF16) NORMC(float, __nv_bfloat16);
+    NORMC(float, float);
+#undef NORMC
 }

@@ -1,0 +1,286 @@
+// Routed experts: every token goes through the `top` experts whose router logits are largest, and
+// their outputs are summed with the softmax over the chosen logits alone.
+//
+//   route    z = W_r h + b in float32, the `top` largest (ties: the lower index), softmax over them
+//   group    the (token, choice) pairs sorted by expert into segments that start at multiples of
+//            64 slots, so that a tile of 64 slots belongs to one expert
+//   up       inner[slot] = act(W_up[e] h[token])            one tile of rows_product a block
+//   down     y[pair] = W_down[e] inner[slot]
+//   combine  out[n] = sum_k weight[n, k] * y[n * top + k]   float32, in the order of the choices
+//
+// Every output element is one chain of multiply-adds over its inputs in ascending order, and a
+// token's result does not depend on which tokens share its tile, its expert or its step.  The
+// number of tiles that are launched depends on the number of tokens only (tiles without an expert
+// return at once), so a step's launches can be replayed from a CUDA graph.
+
+#include "rows_product.cuh"
+
+DE_DEFINE_PDL_SWITCH
+
+namespace {
+
+constexpr int SEG = rows_product::TILE;     // segments of an expert start at multiples of this
+constexpr int MAX_TOP = 32;
+
+// One warp a token.  logits live in shared memory, [warps][experts].
+template <typename T>
+__global__ void route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w,
+                             const float* __restrict__ bias, int n, int width, int experts,
+                             int top, int* __restrict__ chosen, float* __restrict__ weight) {
+    extern __shared__ float zs[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
+    float* z = zs + (size_t)warp * experts;
+    pdl_wait();
+    pdl_trigger();
+    if (row >= n) return;
+    const T* x = h + (size_t)row * ldh;
+    for (int e = 0; e < experts; ++e) {
+        const float* wr = w + (size_t)e * width;
+        float s = 0.0f;
+        for (int i = lane; i < width; i += 32) s = fmaf(to_float(x[i]), wr[i], s);
+        s = warp_sum(s);
+        if (lane == 0) z[e] = s + bias[e];
+    }
+    __syncwarp();
+    float best[MAX_TOP];
+    float total = 0.0f;
+    for (int k = 0; k < top; ++k) {
+        float v = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float c = z[e];
+            if (c > v || (c == v && e < at)) { v = c; at = e; }
+        }
+        if (at == 0x7fffffff) v = -INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ov > v || (ov == v && oa < at)) { v = ov; at = oa; }
+        }
+        best[k] = v;
+        if (lane == 0) {
+            chosen[(size_t)row * top + k] = at;
+            z[at] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) total += expf(best[k] - best[0]);
+    if (lane == 0)
+        for (int k = 0; k < top; ++k)
+            weight[(size_t)row * top + k] = expf(best[k] - best[0]) / total;
+}
+
+// One block.  pair_of [slots] (slots = tiles * SEG), tile_expert [tiles], slot_of [pairs].
+__global__ void group_kernel(const int* __restrict__ chosen, int pairs, int experts, int tiles,
+                             int* __restrict__ pair_of, int* __restrict__ tile_expert,
+                             int* __restrict__ slot_of) {
+    extern __shared__ int sh[];                      // [experts] counts, then [experts] cursors
+    int* count = sh;
+    int* cursor = sh + experts;
+    pdl_wait();                 // the lists may still be read by the layer before
+    pdl_trigger();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
+    for (int t = threadIdx.x; t < tiles; t += blockDim.x) tile_expert[t] = -1;
+    for (int i = threadIdx.x; i < tiles * SEG; i += blockDim.x) pair_of[i] = -1;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        if (e >= 0 && e < experts) atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            cursor[e] = at;
+            const int t = (count[e] + SEG - 1) / SEG;
+            for (int i = 0; i < t; ++i) tile_expert[at / SEG + i] = e;
+            at += t * SEG;
+        }
+    }
+    __syncthreads();
+    // which slot of its expert's segment a pair takes does not matter to its result
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
+        const int e = chosen[p];
+        if (e < 0 || e >= experts) { slot_of[p] = -1; continue; }
+        const int slot = atomicAdd(&cursor[e], 1);
+        pair_of[slot] = p;
+        slot_of[p] = slot;
+    }
+}
+
+// inner[slot, j] = act(sum_i h[token(slot), i] * up[e][j][i]); grid (tiles, column tiles of ff).
+template <typename T>
+__global__ void __launch_bounds__(rows_product::THREADS)
+expert_up_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ up,
+                 const int* __restrict__ pair_of, const int* __restrict__ tile_expert, int top,
+                 int width, int ff, T* __restrict__ inner, int act, int vec_a, int vec_w) {
+    __shared__ __align__(16) float smem[rows_product::SMEM_FLOATS];
+    __shared__ int pair_s[SEG];
+    pdl_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int s0 = blockIdx.x * SEG, c0 = blockIdx.y * rows_product::TILE;
+    if (threadIdx.x < SEG) pair_s[threadIdx.x] = pair_of[s0 + threadIdx.x];
+    __syncthreads();
+    float acc[4][4];
+    rows_product::tile<T, T>(
+        [&](int r) -> const T* {
+            const int p = pair_s[r];
+            return p >= 0 ? h + (size_t)(p / top) * ldh : nullptr;
+        },
+        up + ((size_t)e * ff + c0) * width, width, min(rows_product::TILE, ff - c0), width,
+        vec_a != 0, vec_w != 0, smem, acc);
+    pdl_trigger();
+    const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int r = tr * 4 + i;
+        if (pair_s[r] < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + tc * 4 + j;
+            if (c < ff) inner[(size_t)(s0 + r) * ff + c] = from_float<T>(de_activate(acc[i][j], act));
+        }
+    }
+}
+
+// y[pair, j] = sum_i inner[slot, i] * down[e][j][i]; grid (tiles, column tiles of width).
+template <typename T>
+__global__ void __launch_bounds__(rows_product::THREADS)
+expert_down_kernel(const T* __restrict__ inner, const T* __restrict__ down,
+                   const int* __restrict__ pair_of, const int* __restrict__ tile_expert,
+                   int width, int ff, T* __restrict__ y, int vec_a, int vec_w) {
+    __shared__ __align__(16) float smem[rows_product::SMEM_FLOATS];
+    __shared__ int pair_s[SEG];
+    pdl_wait();
+    const int e = tile_expert[blockIdx.x];
+    if (e < 0) return;
+    const int s0 = blockIdx.x * SEG, c0 = blockIdx.y * rows_product::TILE;
+    if (threadIdx.x < SEG) pair_s[threadIdx.x] = pair_of[s0 + threadIdx.x];
+    __syncthreads();
+    float acc[4][4];
+    rows_product::tile<T, T>(
+        [&](int r) -> const T* {
+            return pair_s[r] >= 0 ? inner + (size_t)(s0 + r) * ff : nullptr;
+        },
+        down + ((size_t)e * width + c0) * ff, ff, min(rows_product::TILE, width - c0), ff,
+        vec_a != 0, vec_w != 0, smem, acc);
+    pdl_trigger();
+    const int tr = threadIdx.x >> 4, tc = threadIdx.x & 15;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const int p = pair_s[tr * 4 + i];
+        if (p < 0) continue;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int c = c0 + tc * 4 + j;
+            if (c < width) y[(size_t)p * width + c] = from_float<T>(acc[i][j]);
+        }
+    }
+}
+
+template <typename T>
+__global__ void combine_kernel(const T* __restrict__ y, const float* __restrict__ weight, int top,
+                               int width, size_t total, float* __restrict__ out) {
+    pdl_wait();
+    pdl_trigger();
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t n = idx / width;
+        const int i = (int)(idx - n * width);
+        float s = 0.0f;
+        for (int k = 0; k < top; ++k)
+            s = fmaf(weight[n * top + k], to_float(y[(n * top + k) * width + i]), s);
+        out[idx] = s;
+    }
+}
+
+}  // namespace
+
+// How many tiles (of 64 slots) the grouped pairs of n tokens can take at most.
+DE_EXPORT int de_experts_tiles(int n, int top, int experts) {
+    const long long pairs = (long long)n * top;
+    const long long most = pairs / SEG + (experts < pairs ? experts : pairs);
+    return (int)(most < 1 ? 1 : most);
+}
+
+DE_EXPORT int de_experts_route(int dtype, const void* h, int ldh, const float* w,
+                               const float* bias, int n, int width, int experts, int top,
+                               int* chosen, float* weight, void* stream) {
+    if (n <= 0) return 0;
+    if (top <= 0 || top > MAX_TOP || top > experts || experts > 4096) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int warps = 4;
+    const size_t smem = (size_t)warps * experts * sizeof(float);
+    const dim3 grid((n + warps - 1) / warps);
+    if (dtype == DE_BF16)
+        return de_launch(route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, s,
+                         (const __nv_bfloat16*)h, ldh, w, bias, n, width, experts, top, chosen,
+                         weight);
+    return de_launch(route_kernel<float>, grid, dim3(warps * 32), smem, s, (const float*)h, ldh, w,
+                     bias, n, width, experts, top, chosen, weight);
+}
+
+DE_EXPORT int de_experts_group(const int* chosen, int pairs, int experts, int tiles, int* pair_of,
+                               int* tile_expert, int* slot_of, void* stream) {
+    if (pairs <= 0) return 0;
+    if (experts > 4096) return -2;
+    return de_launch(group_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int),
+                     (cudaStream_t)stream, chosen, pairs, experts, tiles, pair_of, tile_expert,
+                     slot_of);
+}
+
+DE_EXPORT int de_experts_up(int dtype, const void* h, int ldh, const void* up, const int* pair_of,
+                            const int* tile_expert, int tiles, int top, int width, int ff,
+                            void* inner, int act, void* stream) {
+    if (tiles <= 0) return 0;
+    if (act < 0 || act > 4) return -2;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int size = dtype == DE_BF16 ? 2 : 4;
+    const int vec_a = ((uintptr_t)h % (4 * size) == 0) && ldh % 4 == 0;
+    const int vec_w = ((uintptr_t)up % (4 * size) == 0) && width % 4 == 0;
+    const dim3 grid(tiles, (ff + rows_product::TILE - 1) / rows_product::TILE);
+    if (grid.y > 65535) return -2;
+    if (dtype == DE_BF16)
+        return de_launch(expert_up_kernel<__nv_bfloat16>, grid, dim3(rows_product::THREADS), 0, s,
+                         (const __nv_bfloat16*)h, ldh, (const __nv_bfloat16*)up, pair_of,
+                         tile_expert, top, width, ff, (__nv_bfloat16*)inner, act, vec_a, vec_w);
+    return de_launch(expert_up_kernel<float>, grid, dim3(rows_product::THREADS), 0, s,
+                     (const float*)h, ldh, (const float*)up, pair_of, tile_expert, top, width, ff,
+                     (float*)inner, act, vec_a, vec_w);
+}
+
+DE_EXPORT int de_experts_down(int dtype, const void* inner, const void* down, const int* pair_of,
+                              const int* tile_expert, int tiles, int width, int ff, void* y,
+                              void* stream) {
+    if (tiles <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int size = dtype == DE_BF16 ? 2 : 4;
+    const int vec_a = ((uintptr_t)inner % (4 * size) == 0) && ff % 4 == 0;
+    const int vec_w = ((uintptr_t)down % (4 * size) == 0) && ff % 4 == 0;
+    const dim3 grid(tiles, (width + rows_product::TILE - 1) / rows_product::TILE);
+    if (grid.y > 65535) return -2;
+    if (dtype == DE_BF16)
+        return de_launch(expert_down_kernel<__nv_bfloat16>, grid, dim3(rows_product::THREADS), 0,
+                         s, (const __nv_bfloat16*)inner, (const __nv_bfloat16*)down, pair_of,
+                         tile_expert, width, ff, (__nv_bfloat16*)y, vec_a, vec_w);
+    return de_launch(expert_down_kernel<float>, grid, dim3(rows_product::THREADS), 0, s,
+                     (const float*)inner, (const float*)down, pair_of, tile_expert, width, ff,
+                     (float*)y, vec_a, vec_w);
+}
+
+DE_EXPORT int de_experts_combine(int dtype, const void* y, const float* weight, int n, int top,
+                                 int width, float* out, void* stream) {
+    if (n <= 0) return 0;
+    const size_t total = (size_t)n * width;
+    size_t blocks = (total + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
+                         (const __nv_bfloat16*)y, weight, top, width, total, out);
+    return de_launch(combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s,
+                     (const float*)y, weight, top, width, total, out);
+}

@@ -40,6 +40,8 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "attention_tcgen05": ("attention_tcgen05.cu", ()),  # built per head size: HEAD_DIM=64|128
     "attention_chunk": ("attention_chunk.cu", ()),
     "recurrent": ("recurrent.cu", ()),
+    "latent": ("latent.cu", ()),
+    "experts": ("experts.cu", ()),
 }
 
 

@@ -1,0 +1,138 @@
+"""Tensor-level wrappers of the latent-attention kernels (``csrc/latent.cu``) and of the routed
+experts (``csrc/experts.cu``)."""
+
+from __future__ import annotations
+
+import torch
+
+from . import library
+from .ops import ACTIVATIONS, _check, _i32, _need, _ptr, _stream, _tag
+
+
+def latent_write(q: torch.Tensor, kv: torch.Tensor, qa: torch.Tensor, freq: torch.Tensor,
+                 magnitude: float, norm_weight: torch.Tensor, eps: float, heads: int, dim: int,
+                 rot: int, rank: int, pages: torch.Tensor, block_table: torch.Tensor, ctx) -> None:
+    """Per token: the latent c = rms_norm(kv[:, :rank]) * norm_weight and the key part kv[:, rank:]
+    turned by the token's position go to the pages ([pages, 1, page, rank + rot]); every head's
+    rotated query part (q rows are heads of [dim | rot]) goes, turned, to columns rank.. of its
+    head in ``qa`` (rows of heads of [rank | rot]).  ``freq`` float64 [rot / 2]; cosine and sine
+    are multiplied by ``magnitude``."""
+    n = q.shape[0]
+    _need(q.stride(1) == 1 and kv.stride(1) == 1 and qa.stride(1) == 1
+          and q.shape[1] >= heads * (dim + rot) and kv.shape == (n, rank + rot)
+          and qa.shape == (n, heads * (rank + rot)) and q.dtype == kv.dtype == qa.dtype
+          == pages.dtype, "latent_write: q [N, H (dim + rot)], kv [N, rank + rot], qa "
+          "[N, H (rank + rot)] of the pages' dtype")
+    _need(pages.is_contiguous() and pages.dim() == 4 and pages.shape[1] == 1
+          and pages.shape[3] == rank + rot, "latent_write: pages [pages, 1, page, rank + rot]")
+    _need(freq.dtype == torch.float64 and freq.is_contiguous() and freq.shape == (rot // 2,)
+          and rot % 2 == 0, "latent_write: freq float64 [rot / 2]")
+    _need(norm_weight.is_contiguous() and norm_weight.shape == (rank,), "latent_write: weight")
+    _i32(block_table, "block_table")
+    lib = library.load("latent")
+    _check(lib.de_latent_write(_tag(q.dtype), _tag(norm_weight.dtype), q.data_ptr(), q.stride(0),
+                               kv.data_ptr(), kv.stride(0), qa.data_ptr(), qa.stride(0),
+                               ctx.positions.data_ptr(), ctx.token_slot.data_ptr(),
+                               freq.data_ptr(), float(magnitude), norm_weight.data_ptr(),
+                               float(eps), heads, dim, rot, rank, pages.data_ptr(),
+                               block_table.data_ptr(), block_table.stride(0), pages.shape[2],
+                               pages.shape[0], n, ctx.status.data_ptr(), _stream()),
+           "latent_write")
+
+
+def heads_product(a: torch.Tensor, a_head: int, w: torch.Tensor, out: torch.Tensor, out_head: int,
+                  gate: "torch.Tensor | None" = None) -> None:
+    """out[n, h * out_head + j] = sum_i a[n, h * a_head + i] * w[h, j, i], float32 sums on the CUDA
+    cores; w [H, cols, depth] contiguous.  ``gate`` [N, H cols] (w's dtype, free row stride): the
+    results are multiplied by its sigmoid.  a may be float32 beside bfloat16 weights."""
+    heads, cols, depth = w.shape
+    n = a.shape[0]
+    _need(w.is_contiguous() and a.stride(1) == 1 and out.stride(1) == 1 and out.shape[0] == n
+          and a.shape[1] >= (heads - 1) * a_head + depth
+          and out.shape[1] >= (heads - 1) * out_head + cols,
+          "heads_product: a [N, >= H a_head], w [H, cols, depth], out [N, >= H out_head]")
+    if gate is not None:
+        _need(gate.dtype == w.dtype and gate.stride(1) == 1 and gate.shape == (n, heads * cols),
+              "heads_product: gate [N, H cols] of w's dtype")
+    lib = library.load("latent")
+    _check(lib.de_heads_product(_tag(a.dtype), _tag(w.dtype), _tag(out.dtype), a.data_ptr(),
+                                a.stride(0), a_head, w.data_ptr(), out.data_ptr(), out.stride(0),
+                                out_head, _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                n, heads, cols, depth, _stream()), "heads_product")
+
+
+# ------------------------------------------------------------------------------- routed experts
+def experts_tiles(n: int, top: int, experts: int) -> int:
+    """The most tiles of 64 slots that the grouped (token, choice) pairs of n tokens take."""
+    return int(library.load("experts").de_experts_tiles(n, top, experts))
+
+
+def experts_route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top: int,
+                  chosen: torch.Tensor, weight: torch.Tensor) -> None:
+    """chosen [N, top] (int32): the experts with the largest logits router h + bias (float32);
+    weight [N, top] (float32): the softmax over those logits alone."""
+    n, experts = h.shape[0], router.shape[0]
+    _i32(chosen, "chosen")
+    _need(h.stride(1) == 1 and router.dtype == bias.dtype == weight.dtype == torch.float32
+          and router.is_contiguous() and router.shape[1] == h.shape[1] and bias.is_contiguous()
+          and bias.shape == (experts,) and chosen.shape == weight.shape == (n, top)
+          and weight.is_contiguous(), "experts_route: h [N, D], router float32 [E, D], bias [E]")
+    lib = library.load("experts")
+    _check(lib.de_experts_route(_tag(h.dtype), h.data_ptr(), h.stride(0), router.data_ptr(),
+                                bias.data_ptr(), n, h.shape[1], experts, top, chosen.data_ptr(),
+                                weight.data_ptr(), _stream()), "experts_route")
+
+
+def experts_group(chosen: torch.Tensor, experts: int, pair_of: torch.Tensor,
+                  tile_expert: torch.Tensor, slot_of: torch.Tensor) -> None:
+    """Sort the pairs by expert: pair_of [tiles * 64] (the pair in a slot, or -1), tile_expert
+    [tiles] (or -1), slot_of [pairs]."""
+    for t, name in ((chosen, "chosen"), (pair_of, "pair_of"), (tile_expert, "tile_expert"),
+                    (slot_of, "slot_of")):
+        _i32(t, name)
+    tiles = tile_expert.shape[0]
+    _need(pair_of.shape == (tiles * 64,) and slot_of.numel() == chosen.numel(),
+          "experts_group: pair_of [tiles * 64], slot_of [pairs]")
+    lib = library.load("experts")
+    _check(lib.de_experts_group(chosen.data_ptr(), chosen.numel(), experts, tiles,
+                                pair_of.data_ptr(), tile_expert.data_ptr(), slot_of.data_ptr(),
+                                _stream()), "experts_group")
+
+
+def experts_up(h: torch.Tensor, up: torch.Tensor, pair_of: torch.Tensor,
+               tile_expert: torch.Tensor, top: int, inner: torch.Tensor, act: str) -> None:
+    """inner[slot] = act(up[e] h[token of the slot's pair]); up [E, ff, D], inner [slots, ff]."""
+    experts, ff, width = up.shape
+    tiles = tile_expert.shape[0]
+    _need(up.is_contiguous() and h.stride(1) == 1 and h.shape[1] == width and inner.is_contiguous()
+          and inner.shape == (tiles * 64, ff) and h.dtype == up.dtype == inner.dtype
+          and act in ACTIVATIONS, "experts_up: h [N, D], up [E, ff, D], inner [slots, ff]")
+    lib = library.load("experts")
+    _check(lib.de_experts_up(_tag(h.dtype), h.data_ptr(), h.stride(0), up.data_ptr(),
+                             pair_of.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff,
+                             inner.data_ptr(), ACTIVATIONS[act], _stream()), "experts_up")
+
+
+def experts_down(inner: torch.Tensor, down: torch.Tensor, pair_of: torch.Tensor,
+                 tile_expert: torch.Tensor, y: torch.Tensor) -> None:
+    """y[pair] = down[e] inner[slot of the pair]; down [E, D, ff], y [pairs, D]."""
+    experts, width, ff = down.shape
+    tiles = tile_expert.shape[0]
+    _need(down.is_contiguous() and inner.is_contiguous() and inner.shape == (tiles * 64, ff)
+          and y.is_contiguous() and y.shape[1] == width and inner.dtype == down.dtype == y.dtype,
+          "experts_down: inner [slots, ff], down [E, D, ff], y [pairs, D]")
+    lib = library.load("experts")
+    _check(lib.de_experts_down(_tag(inner.dtype), inner.data_ptr(), down.data_ptr(),
+                               pair_of.data_ptr(), tile_expert.data_ptr(), tiles, width, ff,
+                               y.data_ptr(), _stream()), "experts_down")
+
+
+def experts_combine(y: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[n] = sum_k weight[n, k] * y[n * top + k] in float32; out float32 [N, D]."""
+    n, top = weight.shape
+    _need(y.is_contiguous() and y.shape == (n * top, out.shape[1]) and out.is_contiguous()
+          and out.dtype == weight.dtype == torch.float32 and out.shape[0] == n
+          and weight.is_contiguous(), "experts_combine: y [N top, D], weight [N, top], out [N, D]")
+    lib = library.load("experts")
+    _check(lib.de_experts_combine(_tag(y.dtype), y.data_ptr(), weight.data_ptr(), n, top,
+                                  out.shape[1], out.data_ptr(), _stream()), "experts_combine")

@@ -33,6 +33,11 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_activation": [I, P, I, P, I, I, I, I, P],
         "de_softcap": [P, L, F, P],
         "de_scaled_sum": [I, P, P, F, F, P, L, P],
+        "de_residual_add": [P, I, P, I, P, P, I, P, L, P],
+        "de_act_mul": [I, P, I, P, I, I, I, I, P],
+        "de_act_mul_row": [I, P, I, P, P, I, P, I, I, I, I, P],
+        "de_add_normed": [I, I, P, P, P, I, I, F, P],
+        "de_rmsnorm_cols": [I, I, P, I, P, P, I, I, I, F, P],
     },
     "gemm_f32": {
         "de_gemm_f32": [P, P, P, I, I, I, I, I, I, P], "de_gemm_f32_small_rows": [],
@@ -70,12 +75,12 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_chunk_rows": [I, I, I, I],
         "de_attn_chunk_decode_ok": [I, I, I, I, I],
         "de_attn_chunk_decode": [I, P, I, P, I, P, P, P, I, I, P, P, P, I, P, P, I, I, I, I, I, F,
-                                 I, I, I, F, I, I, P, I, P, I, P, I, P, P],
+                                 I, I, I, F, I, I, P, I, P, I, P, I, I, P, P],
         "de_kv_write_rotated": [I, P, I, P, P, P, I, P, I, I, I, I, P, P, P, I, I, I, I, I, P, P],
         "de_attn_finish": [I, P, P, P, P, I, P, I, I, I, P],
         "de_kv_write_normed": [I, P, I, I, P, P, I, I, I, F, P, P, P, I, I, I, I, P, P],
         "de_attn_chunk": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F,
-                          I, I, I, F, I, I, P, P],
+                          I, I, I, F, I, I, I, P, P],
     },
     "recurrent": {
         "de_recurrent_max_key_dim": [],
@@ -89,6 +94,19 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_silu_rows": [I, P, I, P, I, I, P],
         "de_head_gate": [I, P, P, I, P, P, I, I, I, F, I, P],
         "de_mean_of_normed": [I, P, P, P, P, P, I, I, F, P],
+    },
+    "latent": {
+        "de_latent_write": [I, I, P, I, P, I, P, I, P, P, P, F, P, F, I, I, I, I, P, P, I, I, I, I,
+                            P, P],
+        "de_heads_product": [I, I, I, P, I, I, P, P, I, I, P, I, I, I, I, I, P],
+    },
+    "experts": {
+        "de_experts_tiles": [I, I, I],
+        "de_experts_route": [I, P, I, P, P, I, I, I, I, P, P, P],
+        "de_experts_group": [P, I, I, I, P, P, P, P],
+        "de_experts_up": [I, P, I, P, P, P, I, I, I, I, P, I, P],
+        "de_experts_down": [I, P, P, P, P, I, I, I, P, P],
+        "de_experts_combine": [I, P, P, I, I, I, P, P],
     },
     "attention_decode": {
         "de_attn_decode_head_dim": [], "de_attn_decode_max_cluster": [],

@@ -143,12 +143,12 @@ def add_layernorm(resid: torch.Tensor, delta: "torch.Tensor | None", weight: tor
 
 
 # ------------------------------------------------------------------------------- element-wise
-ACTIVATIONS = {"relu2": 0, "tanh": 1, "silu": 2, "gelu_tanh": 3}
+ACTIVATIONS = {"relu2": 0, "tanh": 1, "silu": 2, "gelu_tanh": 3, "gelu_erf": 4}
 
 
 def activation(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
     """out = act(x) element by element (float32 arithmetic): ``relu2`` the square of relu,
-    ``tanh``, ``silu``, ``gelu_tanh``.  x and out [N, cols] with free row strides; out may be x."""
+    ``tanh``, ``silu``, ``gelu_tanh``, ``gelu_erf`` (the exact form).  x and out [N, cols] with free row strides; out may be x."""
     _need(kind in ACTIVATIONS, f"activation: unknown kind '{kind}'; known: {sorted(ACTIVATIONS)}")
     _need(x.dim() == 2 and x.shape == out.shape and x.dtype == out.dtype and x.stride(1) == 1
           and out.stride(1) == 1, "activation: x and out [N, cols] of one dtype")
@@ -173,6 +173,76 @@ def scaled_sum(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float, out: torc
     lib = library.load("core")
     _check(lib.de_scaled_sum(_tag(out.dtype), a.data_ptr(), b.data_ptr(), float(sa), float(sb),
                              out.data_ptr(), out.numel(), _stream()), "scaled_sum")
+
+
+def residual_add(resid: torch.Tensor, a: "torch.Tensor | None", b: "torch.Tensor | None" = None,
+                 extra: "torch.Tensor | None" = None,
+                 rows: "torch.Tensor | None" = None) -> None:
+    """resid += (a + b) + extra in float32: ``a`` and ``b`` are branch outputs (bfloat16 or
+    float32, either may be None), ``extra`` is float32; ``rows`` receives the new residual in its
+    own dtype.  All contiguous and of resid's shape."""
+    _need(resid.dtype == torch.float32 and resid.is_contiguous(), "residual_add: resid float32")
+    for t in (a, b, extra, rows):
+        _need(t is None or (t.is_contiguous() and t.shape == resid.shape),
+              "residual_add: operands are contiguous and of resid's shape")
+    _need(extra is None or extra.dtype == torch.float32, "residual_add: extra is float32")
+    if a is None and b is None and extra is None and rows is None:
+        return
+    lib = library.load("core")
+    _check(lib.de_residual_add(resid.data_ptr(), 0 if a is None else _tag(a.dtype), _ptr(a),
+                               0 if b is None else _tag(b.dtype), _ptr(b), _ptr(extra),
+                               0 if rows is None else _tag(rows.dtype), _ptr(rows),
+                               resid.numel(), _stream()), "residual_add")
+
+
+def act_mul(x: torch.Tensor, out: torch.Tensor, kind: str) -> None:
+    """out[n, i] = act(x[n, i]) * x[n, inner + i]; x [N, 2 inner], out [N, inner]."""
+    n, inner = out.shape
+    _need(kind in ACTIVATIONS, f"act_mul: unknown kind '{kind}'")
+    _need(x.stride(1) == 1 and out.stride(1) == 1 and x.shape == (n, 2 * inner)
+          and x.dtype == out.dtype, "act_mul: x must be [N, 2 inner] and out [N, inner]")
+    lib = library.load("core")
+    _check(lib.de_act_mul(_tag(x.dtype), x.data_ptr(), x.stride(0), out.data_ptr(), out.stride(0),
+                          n, inner, ACTIVATIONS[kind], _stream()), "act_mul")
+
+
+def act_mul_row(z: torch.Tensor, ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor,
+                kind: str) -> None:
+    """out[n, i] = act(z[n, i]) * table[ids[n], i]; z, out [N, dim], table [V, dim]."""
+    n, dim = out.shape
+    _i32(ids, "ids")
+    _need(kind in ACTIVATIONS, f"act_mul_row: unknown kind '{kind}'")
+    _need(z.shape == out.shape and z.stride(1) == 1 and out.stride(1) == 1
+          and table.is_contiguous() and table.dim() == 2 and table.shape[1] == dim
+          and z.dtype == out.dtype == table.dtype and ids.shape == (n,),
+          "act_mul_row: z, out [N, dim] and table [V, dim] of one dtype")
+    lib = library.load("core")
+    _check(lib.de_act_mul_row(_tag(z.dtype), z.data_ptr(), z.stride(0), ids.data_ptr(),
+                              table.data_ptr(), table.shape[0], out.data_ptr(), out.stride(0), n,
+                              dim, ACTIVATIONS[kind], _stream()), "act_mul_row")
+
+
+def add_normed(resid: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float) -> None:
+    """resid += y / sqrt(mean(y^2) + eps) * weight row by row, in float32."""
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and y.is_contiguous()
+          and y.shape == resid.shape and weight.is_contiguous()
+          and weight.shape == (resid.shape[1],), "add_normed: resid float32, y and weight")
+    lib = library.load("core")
+    _check(lib.de_add_normed(_tag(y.dtype), _tag(weight.dtype), resid.data_ptr(), y.data_ptr(),
+                             weight.data_ptr(), resid.shape[0], resid.shape[1], float(eps),
+                             _stream()), "add_normed")
+
+
+def rmsnorm_cols(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = x / sqrt(mean(x^2) + eps) * weight over the columns of x [N, cols] (row strides
+    free: x may be a block of columns of a product's output)."""
+    _need(x.dim() == 2 and x.shape == out.shape and x.stride(1) == 1 and out.stride(1) == 1
+          and x.dtype == out.dtype and weight.is_contiguous() and weight.shape == (x.shape[1],),
+          "rmsnorm_cols: x, out [N, cols] of one dtype and weight [cols]")
+    lib = library.load("core")
+    _check(lib.de_rmsnorm_cols(_tag(x.dtype), _tag(weight.dtype), x.data_ptr(), x.stride(0),
+                               weight.data_ptr(), out.data_ptr(), out.stride(0), x.shape[0],
+                               x.shape[1], float(eps), _stream()), "rmsnorm_cols")
 
 
 # ------------------------------------------------------------------------------- rotation + cache write

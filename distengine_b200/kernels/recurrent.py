@@ -282,7 +282,7 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                            r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                            value_dim: int, scale: float, chunk: int, ctx, window: int = 0,
                            keep_first: int = 0, softcap: float = 0.0,
-                           fused: "dict | None" = None) -> None:
+                           fused: "dict | None" = None, v_stride: int = 0) -> None:
     """``chunk_attention`` for a step in which every sequence brings one token: a block a
     (sequence, kv head), its warps share the key tiles out; no work items.
 
@@ -290,7 +290,11 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
     ``kv_write_rotated`` and ``attention_finish`` do around the other kernels - it turns the
     queries (in its own memory: ``q`` stays as it is), turns and stores the token's key and value
     (``q``'s rows are then [q (H dk) | k (G dk) | v (G dv) | ...]), turns every head's result back
-    and gates it; ``out`` has the activation dtype."""
+    and gates it; ``out`` has the activation dtype.
+
+    ``v_stride`` not 0: the values of consecutive keys lie that many elements apart in
+    ``v_pages`` (values that are the first features of the key rows: ``v_pages`` is ``k_pages``
+    and the stride the key size)."""
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == k_pages.dtype
           and out.dtype in (q.dtype, torch.float32)
           and out.shape[1] == heads * value_dim and q.shape[0] == ctx.n_seqs,
@@ -327,7 +331,7 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                                     key_dim, value_dim, k_pages.shape[2], float(scale),
                                     int(chunk), int(window), int(keep_first), float(softcap),
                                     int(out.dtype == torch.float32 and q.dtype != torch.float32),
-                                    *extra, ctx.status.data_ptr(), _stream()),
+                                    *extra, int(v_stride), ctx.status.data_ptr(), _stream()),
            "chunk_attention_decode")
 
 
@@ -357,10 +361,12 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                     v_pages: torch.Tensor, block_table: torch.Tensor, items: torch.Tensor,
                     r1: torch.Tensor, r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                     value_dim: int, scale: float, chunk: int, ctx, tile_rows: int = 8,
-                    window: int = 0, keep_first: int = 0, softcap: float = 0.0) -> None:
+                    window: int = 0, keep_first: int = 0, softcap: float = 0.0,
+                    v_stride: int = 0) -> None:
     """Attention of the step's rows over the pages: q rows of [heads dk] at the front of ``q``
     (row stride free), out [N, heads dv]; ``tile_rows``: the rows of a tile that ``items`` were
-    cut for (``chunk_rows_per_tile``); see ``csrc/attention_chunk.cu``."""
+    cut for (``chunk_rows_per_tile``); ``v_stride`` as in ``chunk_attention_decode``; see
+    ``csrc/attention_chunk.cu``."""
     _need(q.stride(1) == 1 and out.stride(1) == 1 and q.dtype == k_pages.dtype
           and out.dtype in (q.dtype, torch.float32)
           and out.shape[1] == heads * value_dim, "chunk_attention: q, out and pages")
@@ -376,7 +382,8 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                              key_dim, value_dim, k_pages.shape[2], float(scale), int(chunk),
                              int(window), int(keep_first), float(softcap),
                              int(out.dtype == torch.float32 and q.dtype != torch.float32),
-                             int(tile_rows), ctx.status.data_ptr(), _stream()), "chunk_attention")
+                             int(tile_rows), int(v_stride), ctx.status.data_ptr(), _stream()),
+           "chunk_attention")
 
 
 def kv_write_rotated(proj: torch.Tensor, fk: torch.Tensor, rotary_dim: int,

@@ -13,7 +13,7 @@ import torch
 from ..config.model import LayerSpec, ModelConfig
 from ..kernels import library, ops
 from ..parts.base import (Block, PagedKVSpec, StateSpec, build_block, build_feed_forward,
-                          build_mixer, build_norm, compute_matrix)
+                          build_mixer, build_norm, build_side_input, compute_matrix)
 from ..parts.context import CacheBinding, ResidualStream, StepContext, StepPrep
 
 
@@ -22,8 +22,17 @@ def _layer_parts(spec: LayerSpec, dtype: torch.dtype, device: torch.device) -> B
     if spec.feed_forward is not None:
         feed_forward = build_feed_forward(spec.feed_forward, dtype, device)
         feed_forward_norm = build_norm(spec.feed_forward_norm or spec.norm, dtype, device)
+    side_input = None
+    if spec.side_input is not None:
+        side_input = build_side_input(spec.side_input, dtype, device)
     return build_block(spec.block, build_mixer(spec.mixer, dtype, device), feed_forward,
-                       build_norm(spec.norm, dtype, device), feed_forward_norm)
+                       build_norm(spec.norm, dtype, device), feed_forward_norm, side_input)
+
+
+def _full_name(prefix: str, local: str) -> str:
+    """A part's tensor in the weight file: under the part's prefix, or, for a local name that
+    starts with "/", the name behind the slash as it is."""
+    return local[1:] if local.startswith("/") else prefix + local
 
 
 class DecoderModel:
@@ -54,7 +63,9 @@ class DecoderModel:
         for spec, block in zip(self.specs, self.blocks):
             for role, part in block.parts().items():
                 for local, (shape, kind) in part.tensors().items():
-                    full = spec.prefix(role) + local
+                    full = _full_name(spec.prefix(role), local)
+                    if expected.get(full, tuple(shape)) != tuple(shape):
+                        raise ValueError(f"tensor '{full}' is expected in two shapes")
                     expected[full] = tuple(shape)
                     if kind == "vector":
                         vectors.add(full)
@@ -85,7 +96,8 @@ class DecoderModel:
         for spec, block in zip(self.specs, self.blocks):
             for role, part in block.parts().items():
                 prefix = spec.prefix(role)
-                part.load({local: tensors[prefix + local] for local in part.tensors()})
+                part.load({local: tensors[_full_name(prefix, local)]
+                           for local in part.tensors()})
         self.final_norm.load({local: tensors[names["final_norm"] + local]
                               for local in self.final_norm.tensors()})
         if names["output"] in tensors:
@@ -146,11 +158,21 @@ class DecoderModel:
         resid = ctx.buffer("model.residual", (ctx.n_tokens, self.config.width), torch.float32)
         ops.embed_rows(ctx.token_ids, self.embedding, resid, self.config.embedding_scale)
         stream = ResidualStream(resid)
+        first = None
+        if any(entry.adds_embedding for entry in self.plan):
+            first = ctx.buffer("model.embedding", (ctx.n_tokens, self.config.width),
+                               torch.float32)
+            ops.embed_rows(ctx.token_ids, self.embedding, first, self.config.embedding_scale)
         for index, entry in enumerate(self.plan):
+            if entry.adds_embedding:
+                if stream.ahead is not None:
+                    raise RuntimeError("a pass cannot start while a norm's work is handed ahead")
+                ops.residual_add(stream.resid, stream.pending, None, first)
+                stream.pending = None
             # the norm and mixer that read the stream next, for blocks that hand a norm's work to
             # the product before it
             following = None
-            if index + 1 < len(self.plan):
+            if index + 1 < len(self.plan) and not self.plan[index + 1].adds_embedding:
                 later = self.blocks[self.plan[index + 1].layer]
                 following = (later.mixer_norm, later.mixer)
             self.blocks[entry.layer].forward(stream, ctx, caches[index], following=following)

@@ -1,13 +1,16 @@
-from . import (attention, block, chunk_attention, mlp, norm, parallel,  # noqa: F401
-               recurrent, rope, window_attention)  # (register the built-in kinds)
+from . import (attention, block, chunk_attention, experts, latent_attention,  # noqa: F401
+               mlp, norm, parallel, recurrent, rope, token_side,
+               window_attention)  # (register the built-in kinds)
 from .base import (Block, FeedForward, Mixer, Norm, PagedKVSpec, Part, PositionEncoding,
                    StateSpec, build_block, build_feed_forward, build_mixer, build_norm,
                    build_position_encoding, register_block, register_feed_forward,
-                   register_mixer, register_norm, register_position_encoding)
+                   register_mixer, register_norm, register_position_encoding,
+                   register_side_input)
 from .context import CacheBinding, ResidualStream, StepContext, StepPrep, Workspace
 
 __all__ = ["Block", "FeedForward", "Mixer", "Norm", "PagedKVSpec", "Part", "PositionEncoding",
            "StateSpec", "build_block", "build_feed_forward", "build_mixer", "build_norm",
            "build_position_encoding", "register_block", "register_feed_forward",
-           "register_mixer", "register_norm", "register_position_encoding", "CacheBinding",
+           "register_mixer", "register_norm", "register_position_encoding",
+           "register_side_input", "CacheBinding",
            "ResidualStream", "StepContext", "StepPrep", "Workspace"]

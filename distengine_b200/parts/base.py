@@ -2,8 +2,8 @@
 
 A part knows its own sizes and constants (constructor arguments, from a ``PartSpec``), the tensors
 it needs from the weight file (by local name) and how to run on the tokens of a step.  It does not
-know which model it is in.  Kinds are looked up in four registries - mixers, feed-forwards, norms,
-position encodings - plus one for block arrangements; a new kind is one ``register_*`` call, from
+know which model it is in.  Kinds are looked up in five registries - mixers, feed-forwards, norms,
+position encodings, side inputs - plus one for block arrangements; a new kind is one ``register_*`` call, from
 anywhere (a test registers a toy mixer without touching this package).
 
 The reference has the same separation of primitives whose constants are constructor parameters
@@ -30,13 +30,16 @@ class PagedKVSpec:
     ``chunk``: a token reads keys of its own chunk of positions only (chunks of this many
     positions, counted from 0), so pages that lie wholly before the chunk of the next position are
     given back.  ``keep_first``: with a window, the first this many keys of a sequence stay
-    readable for ever, so the pages that hold them are never given back while the request lives."""
+    readable for ever, so the pages that hold them are never given back while the request lives.
+    ``values_in_keys``: the values are the first ``value_dim`` features of the key rows (a latent
+    that serves as both), so there are no value pages: the binding's ``v_pages`` is ``k_pages``."""
     kv_heads: int
     head_dim: int
     window: int | None = None
     value_dim: int | None = None
     chunk: int | None = None
     keep_first: int = 0
+    values_in_keys: bool = False
 
     @property
     def v_dim(self) -> int:
@@ -69,7 +72,8 @@ class Part:
 
     def tensors(self) -> dict[str, tuple[tuple[int, ...], str]]:
         """local tensor name -> (shape, "matrix" | "vector").  Matrices are drawn N(0, 0.02) in
-        the random-weights mode, vectors are norm weights."""
+        the random-weights mode, vectors are norm weights.  A name that starts with "/" is the
+        tensor's whole name in the weight file (a table that several layers share)."""
         return {}
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
@@ -145,19 +149,31 @@ class FeedForward(Part, NormRider):
         raise NotImplementedError
 
 
+class SideInput(Part):
+    """What a layer adds to the stream from the token itself, after its branches."""
+
+    def forward(self, stream: ResidualStream, rows: torch.Tensor, ctx: StepContext) -> None:
+        """``stream.resid`` is complete (nothing pending) and ``rows`` is its copy in the
+        activation dtype; add this part's output to ``stream.resid``."""
+        raise NotImplementedError
+
+
 class Block:
     """Arrangement of a mixer, a feed-forward and their norms around the residual stream."""
 
     def __init__(self, mixer: Mixer, feed_forward: "FeedForward | None", mixer_norm: Norm,
-                 feed_forward_norm: "Norm | None") -> None:
-        """``feed_forward`` and its norm are None in a layer that has a mixer only."""
+                 feed_forward_norm: "Norm | None", side_input: "SideInput | None" = None) -> None:
+        """``feed_forward`` and its norm are None in a layer that has a mixer only;
+        ``side_input`` only in arrangements that take one."""
         self.mixer, self.feed_forward = mixer, feed_forward
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
+        self.side_input = side_input
 
     def parts(self) -> dict[str, Part]:
         """role -> part; the roles are the keys of ``LayerSpec.prefixes``."""
         parts = {"mixer": self.mixer, "feed_forward": self.feed_forward,
-                 "mixer_norm": self.mixer_norm, "feed_forward_norm": self.feed_forward_norm}
+                 "mixer_norm": self.mixer_norm, "feed_forward_norm": self.feed_forward_norm,
+                 "side_input": self.side_input}
         return {role: part for role, part in parts.items() if part is not None}
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
@@ -175,6 +191,7 @@ MIXERS: dict[str, PartFactory] = {}
 FEED_FORWARDS: dict[str, PartFactory] = {}
 NORMS: dict[str, PartFactory] = {}
 POSITION_ENCODINGS: dict[str, PartFactory] = {}
+SIDE_INPUTS: dict[str, PartFactory] = {}
 BLOCKS: dict[str, Callable[..., Block]] = {}
 
 
@@ -198,6 +215,10 @@ def register_norm(kind: str, factory: PartFactory) -> None:
 
 def register_position_encoding(kind: str, factory: PartFactory) -> None:
     _register(POSITION_ENCODINGS, "position encoding", kind, factory)
+
+
+def register_side_input(kind: str, factory: PartFactory) -> None:
+    _register(SIDE_INPUTS, "side input", kind, factory)
 
 
 def register_block(kind: str, factory: Callable[..., Block]) -> None:
@@ -229,11 +250,17 @@ def build_position_encoding(spec: PartSpec, dtype: torch.dtype,
                   device)                                        # type: ignore[return-value]
 
 
+def build_side_input(spec: PartSpec, dtype: torch.dtype, device: torch.device) -> SideInput:
+    return _build(SIDE_INPUTS, "side input", spec, dtype, device)  # type: ignore[return-value]
+
+
 def build_block(kind: str, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                feed_forward_norm: Norm) -> Block:
+                feed_forward_norm: Norm, side_input: "SideInput | None" = None) -> Block:
     if kind not in BLOCKS:
         raise ValueError(f"unknown block kind '{kind}'; registered: {sorted(BLOCKS)}")
-    return BLOCKS[kind](mixer, feed_forward, mixer_norm, feed_forward_norm)
+    if side_input is None:
+        return BLOCKS[kind](mixer, feed_forward, mixer_norm, feed_forward_norm)
+    return BLOCKS[kind](mixer, feed_forward, mixer_norm, feed_forward_norm, side_input)
 
 
 def compute_matrix(tensor: torch.Tensor, dtype: torch.dtype, device: torch.device) -> torch.Tensor:

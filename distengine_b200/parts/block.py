@@ -1,9 +1,12 @@
 """Pre-norm block: x += mixer(norm(x)); x += feed_forward(norm(x))
 (src/models/llama.py:66-89).  The sums are carried as the stream's pending branch and folded in
-by the next norm.  A layer without a feed-forward is the first half only."""
+by the next norm.  A layer without a feed-forward is the first half only.
+
+``parallel_norms``: both branches read the same x (see ``ParallelNormsBlock``)."""
 
 from __future__ import annotations
 
+from ..kernels import ops
 from .base import Block, register_block
 from .context import CacheBinding, ResidualStream, StepContext
 
@@ -60,3 +63,30 @@ def _ahead(producer, norm, consumer, stream: ResidualStream, ctx: StepContext):
 
 
 register_block("prenorm", PreNormBlock)
+
+
+class ParallelNormsBlock(Block):
+    """Two branches of the same input, each behind a norm of its own:
+    x += mixer(norm1(x)) + feed_forward(norm2(x)), the three terms summed in float32; then the
+    layer's side input, if it has one, reads the new x and adds to it.  A layer without a
+    feed-forward is x += mixer(norm1(x))."""
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
+                following=None) -> None:
+        if stream.ahead is not None:
+            raise RuntimeError("a block of parallel branches runs its norms itself")
+        h = self.mixer_norm.forward(stream, ctx)            # also folds what was pending
+        h2 = None
+        if self.feed_forward is not None:
+            h2 = self.feed_forward_norm.forward(stream, ctx, out_name="norm.out.second")
+        a = self.mixer.forward(h, ctx, cache)
+        b = self.feed_forward.forward(h2, ctx) if self.feed_forward is not None else None
+        if self.side_input is None:
+            ops.residual_add(stream.resid, a, b)
+            return
+        rows = ctx.buffer("block.rows", tuple(stream.resid.shape))
+        ops.residual_add(stream.resid, a, b, rows=rows)
+        self.side_input.forward(stream, rows, ctx)
+
+
+register_block("parallel_norms", ParallelNormsBlock)

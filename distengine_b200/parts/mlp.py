@@ -1,4 +1,5 @@
-"""Dense gated feed-forward (SwiGLU): down( silu(gate(x)) * up(x) ), no biases
+"""Dense gated feed-forward: down( act(gate(x)) * up(x) ), no biases; act is silu (SwiGLU,
+fused into the products) or any other of ``ops.ACTIVATIONS`` (a kernel after the product)
 (src/models/llama.py:13-29, src/layers/activation.py:6-9).  gate and up are one product against
 the stacked matrix [2 inner, width]; the reference runs two and concatenates (llama.py:23-26).
 """
@@ -20,9 +21,10 @@ class GatedMLP(FeedForward):
         """``names``: the local names of the gate, up and down matrices."""
         super().__init__(dtype, device)
         self.names = tuple(names)
-        if activation != "silu":
-            raise ValueError(f"gated_mlp: activation '{activation}' is not implemented; 'silu' is")
-        self.width, self.inner = width, inner
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"gated_mlp: activation '{activation}' is not implemented; "
+                             f"{sorted(ops.ACTIVATIONS)} are")
+        self.width, self.inner, self.activation = width, inner, activation
         self.w_gate_up: "torch.Tensor | None" = None
         self.w_down: "torch.Tensor | None" = None
 
@@ -39,7 +41,9 @@ class GatedMLP(FeedForward):
         self.w_down = compute_matrix(tensors[down], self.dtype, self.device)
 
     def takes_unscaled(self, n_rows: int) -> bool:
-        return ops.norm_ride_parts(n_rows, self.w_gate_up, self.dtype) > 0
+        # the products' fused gate is the silu one
+        return (self.activation == "silu"
+                and ops.norm_ride_parts(n_rows, self.w_gate_up, self.dtype) > 0)
 
     def ahead_parts(self, n_rows: int) -> int:
         return ops.norm_ride_parts(n_rows, self.w_down, self.dtype)
@@ -52,9 +56,15 @@ class GatedMLP(FeedForward):
         n = x.shape[0]
         act = ctx.buffer("mlp.act", (n, self.inner))
         scratch = None
-        if before is None and ops.gated_needs_scratch(x, self.w_gate_up):
+        if self.activation != "silu":
+            # another gate than the products' own: the product, then the gate as a kernel
             scratch = ctx.buffer("mlp.gate_up", (n, 2 * self.inner))
-        ops.linear_gated(x, self.w_gate_up, act, scratch, status=ctx.status, before=before)
+            ops.linear(x, self.w_gate_up, out=scratch, status=ctx.status)
+            ops.act_mul(scratch, act, self.activation)
+        else:
+            if before is None and ops.gated_needs_scratch(x, self.w_gate_up):
+                scratch = ctx.buffer("mlp.gate_up", (n, 2 * self.inner))
+            ops.linear_gated(x, self.w_gate_up, act, scratch, status=ctx.status, before=before)
         if ahead is not None:          # the product joins the residual and does the next norm's work
             ops.linear(act, self.w_down, out=ahead.rows, status=ctx.status, after=ahead)
             return None
