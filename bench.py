@@ -813,6 +813,292 @@ def workload_sebilorn(args, warmup: int, steps: int) -> int:
     return 0
 
 
+def vapelix_shape(layers: int) -> dict:
+    """A Vapelix model of the headline's width and vocabulary: latent attention (16 heads of 128
+    plain and 64 rotated query/key features, a latent of 256) in every layer, beside a gated dense
+    feed-forward of the headline's size in every fourth layer and 16 routed experts, 4 a token,
+    in the others (as many active feed-forward weights as the dense layers have); the token's
+    side input after every layer.  No loop, so that the layer runs equal the other models'."""
+    rot = {"dims": 64, "base": 10000.0,
+           "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    mixer = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 256,
+             "scale": 192 ** -0.5, "rot": rot}
+    dense = {"kind": "dense", "ff": MODEL["intermediate_size"]}
+    routed = {"kind": "moe", "expert": {"ff": 2048}, "router": {"experts": 16, "top": 4}}
+    return {"architecture": "Vapelix", "vocab": MODEL["vocab_size"], "width": MODEL["hidden_size"],
+            "norm": {"eps": 1e-6}, "token_side": {"dim": 64},
+            "layers": [{"type": "latent_attention", "mixer": mixer,
+                        "mlp": dense if i % 4 == 0 else routed} for i in range(layers)]}
+
+
+def vapelix_folder(layers: int) -> str:
+    from distengine_b200.weights import write_random_model
+    folder = os.path.join(tempfile.gettempdir(), f"distengine_b200-bench-{os.getuid()}",
+                          f"vapelix-shape-{layers}-layers-seed0-bf16")
+    marker = os.path.join(folder, ".complete")
+    if not os.path.isfile(marker):
+        print("[bench] writing the random-weights model folder ...", file=sys.stderr, flush=True)
+        write_random_model(vapelix_shape(layers), folder, seed=0, dtype="bfloat16",
+                           norm_init="uniform")
+        with open(marker, "w") as handle:
+            handle.write("ok")
+    return folder
+
+
+def vapelix_kernels(peak: dict) -> list[dict]:
+    """The design's kernels alone at the sizes of ``vapelix_shape``, for a prompt of 2,048 tokens
+    and for a decode step of 64 sequences at position 600, each beside the like kernel of the
+    other models at the like size (``like``): attention over the latent beside attention over
+    keys and values of 4 heads of 128, the experts' products beside the dense products of as many
+    active weights, the per-head products beside a dense product of as many flops."""
+    from types import SimpleNamespace
+    import numpy as np
+    import torch
+    from distengine_b200.kernels import latent as lk
+    from distengine_b200.kernels import ops
+    from distengine_b200.kernels import recurrent as rk
+    from distengine_b200.kernels.attention_plan import build_plan
+    from distengine_b200.parts.latent_attention import stretched_frequencies
+    dev, bf16, f32 = "cuda:0", torch.bfloat16, torch.float32
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fp32_peak = 148 * 128 * 2 * 1.965e9          # fused multiply-adds of the CUDA cores
+    tensor_peak = peak["bf16_tflops"] * 1e12
+
+    def ctx_of(lens, pos0):
+        lens = np.asarray(lens, dtype=np.int32)
+        pos0 = np.asarray(pos0, dtype=np.int32)
+        qstart = (np.cumsum(lens) - lens).astype(np.int32)
+        seq = np.repeat(np.arange(len(lens), dtype=np.int32), lens)
+        slots = np.arange(len(lens), dtype=np.int32)
+        pos = pos0[seq] + np.arange(lens.sum(), dtype=np.int32) - qstart[seq]
+        d = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+        return SimpleNamespace(n_seqs=len(lens), token_seq=d(seq), token_slot=d(slots[seq]),
+                               positions=d(pos), seq_slot=d(slots), seq_qstart=d(qstart),
+                               seq_qlen=d(lens), seq_pos0=d(pos0),
+                               host=SimpleNamespace(seq_qlen=lens, seq_pos0=pos0),
+                               status=torch.zeros(1, dtype=torch.int32, device=dev))
+
+    def timed(fn, repeats=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(repeats):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times)
+
+    out = []
+
+    def record(name, case, us, bytes_=0, flops=0, tensor_flops=0, like=""):
+        entry = {"kernel": name, "case": case, "us": round(us, 1), "like": like}
+        bounds = {"hbm": bytes_ / (peak["hbm_gbs"] * 1e3), "fp32 fma": flops / fp32_peak * 1e6,
+                  "tensor": tensor_flops / tensor_peak * 1e6}
+        entry["bound"] = max(bounds, key=bounds.get)
+        entry["roofline_us"] = round(bounds[entry["bound"]], 1)
+        entry["frac"] = round(bounds[entry["bound"]] / us, 3)
+        out.append(entry)
+    shape = vapelix_shape(2)
+    m, routed = shape["layers"][0]["mixer"], shape["layers"][1]["mlp"]
+    H, dim, rot, dv, qr, rank = (m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["q_rank"],
+                                 m["kv_rank"])
+    row, width, ff = rank + rot, MODEL["hidden_size"], MODEL["intermediate_size"]
+    E, top, eff, side = (routed["router"]["experts"], routed["router"]["top"],
+                         routed["expert"]["ff"], shape["token_side"]["dim"])
+    page = PAGE
+    sc = m["rot"]["scaling"]
+    freq, magnitude = stretched_frequencies(m["rot"]["base"], rot, (sc["factor"], sc["original"],
+                                                                    sc["fast"], sc["slow"]))
+    freq = freq.to(dev)
+    w = lambda *s: (torch.randn(*s, device=dev) / s[-1] ** 0.5).to(bf16)
+    for case, lens, pos0 in (("prompt of 2,048", [2048], [0]), ("decode, 64 sequences", [1] * 64,
+                                                                 [600] * 64)):
+        ctx = ctx_of(lens, pos0)
+        n, s = int(sum(lens)), len(lens)
+        longest = max(p + l for p, l in zip(pos0, lens))
+        pages_seq = (longest + page - 1) // page
+        table = torch.arange(s * pages_seq, dtype=torch.int32, device=dev).view(s, pages_seq)
+        keys = sum(sum(p + i + 1 for i in range(l)) for p, l in zip(pos0, lens))
+        read = sum(p + l for p, l in zip(pos0, lens))
+        # ---- latent attention
+        q = torch.randn(n, H * (dim + rot), device=dev).to(bf16)
+        kv = torch.randn(n, row, device=dev).to(bf16)
+        folded = torch.empty(n, H * row, dtype=bf16, device=dev)
+        pages = torch.randn(s * pages_seq, 1, page, row, device=dev).to(bf16)
+        n_kv = torch.rand(rank, device=dev).to(bf16)
+        us = timed(lambda: lk.latent_write(q, kv, folded, freq, magnitude, n_kv, 1e-6, H, dim, rot,
+                                           rank, pages, table, ctx))
+        record("latent_write", case, us, bytes_=n * (H * rot * 4 + 2 * row * 2),
+               like="kv_write_rotated")
+        w_uk_t, w_uv = w(H, rank, dim), w(H, dv, rank)
+        us = timed(lambda: lk.heads_product(q, dim + rot, w_uk_t, folded, row))
+        record("heads_product (keys folded into the query)", case, us,
+               bytes_=n * H * (dim + rank) * 2 + H * rank * dim * 2, flops=2 * n * H * dim * rank,
+               like="linear")
+        mixed = torch.empty(n, H * rank, device=dev)
+        if n == s and rk.chunk_decode_ok(bf16, H, 1, row, rank):
+            us = timed(lambda: rk.chunk_attention_decode(folded, mixed, pages, pages, table, None,
+                                                         None, H, 1, row, rank, m["scale"], 0, ctx,
+                                                         v_stride=row))
+        else:
+            rows = rk.chunk_rows_per_tile(bf16, row, rank, n > s,
+                                          rk.long_portion_rows(ctx.host.seq_qlen, H, 1))
+            plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H, 1, rows, 0, chunk=0)
+            items = torch.from_numpy(plan.items).to(dev)
+            us = timed(lambda: rk.chunk_attention(folded, mixed, pages, pages, table, items, None,
+                                                  None, H, 1, row, rank, m["scale"], 0, ctx,
+                                                  tile_rows=rows, v_stride=row))
+        record("attention over the latent", case, us, bytes_=read * row * 2 + n * H * (row * 2 + rank * 4),
+               flops=2 * keys * H * (row + rank), like="attention, 4 key/value heads of 128")
+        # the like kernel: 16 heads on 4 key/value heads of 128, every earlier token seen
+        G, dk = 4, 128
+        kp = torch.randn(s * pages_seq, G, page, dk, device=dev).to(bf16)
+        vp = torch.randn(s * pages_seq, G, page, dk, device=dev).to(bf16)
+        aq = torch.randn(n, H * dk, device=dev).to(bf16)
+        raw = torch.empty(n, H * dk, device=dev)
+        if n == s and rk.chunk_decode_ok(bf16, H, G, dk, dk):
+            us = timed(lambda: rk.chunk_attention_decode(aq, raw, kp, vp, table, None, None, H, G,
+                                                         dk, dk, 0.09, 0, ctx))
+        else:
+            rows = rk.chunk_rows_per_tile(bf16, dk, dk, n > s,
+                                          rk.long_portion_rows(ctx.host.seq_qlen, H, G))
+            plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, rows, 0, chunk=0)
+            items = torch.from_numpy(plan.items).to(dev)
+            us = timed(lambda: rk.chunk_attention(aq, raw, kp, vp, table, items, None, None, H, G,
+                                                  dk, dk, 0.09, 0, ctx, tile_rows=rows))
+        record("attention, 4 key/value heads of 128 (other models)", case, us,
+               bytes_=read * G * 2 * dk * 2 + n * H * dk * 6, flops=2 * keys * H * 2 * dk)
+        gate = torch.randn(n, H * dv, device=dev).to(bf16)
+        context = torch.empty(n, H * dv, dtype=bf16, device=dev)
+        us = timed(lambda: lk.heads_product(mixed, rank, w_uv, context, dv, gate=gate))
+        record("heads_product (values, gated)", case, us,
+               bytes_=n * H * (rank * 4 + dv * 4) + H * rank * dv * 2, flops=2 * n * H * dv * rank,
+               like="linear")
+        x = torch.randn(n, width, device=dev).to(bf16)
+        w_like = w(H * rank, width)
+        y_like = torch.empty(n, H * rank, dtype=bf16, device=dev)
+        us = timed(lambda: ops.linear(x, w_like, out=y_like))
+        record("linear, 2,048 to 4,096 features (other models)", case, us,
+               bytes_=(n * (width + H * rank) + H * rank * width) * 2,
+               tensor_flops=2 * n * width * H * rank)
+        # ---- routed experts: 16 experts of 2,048 inner features, 4 a token
+        router, bias = torch.randn(E, width, device=dev) / width ** 0.5, torch.zeros(E, device=dev)
+        up, down = w(E, eff, width), w(E, width, eff)
+        tensor = lk.experts_tensor_ok(x, up, n * top)
+        seg = lk.SEGMENT_TENSOR if tensor else lk.SEGMENT
+        tiles = lk.experts_tiles(n, top, E, seg)
+        chosen = torch.empty(n, top, dtype=torch.int32, device=dev)
+        weight = torch.empty(n, top, device=dev)
+        pair_of = torch.empty(tiles * seg, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+        slot_of = torch.empty(n * top, dtype=torch.int32, device=dev)
+        inner = torch.empty(tiles * seg, eff, dtype=bf16, device=dev)
+        rows_ = torch.empty(tiles * seg, width, dtype=bf16, device=dev)
+        y = torch.empty(n * top, width, dtype=bf16, device=dev)
+        eo = torch.empty(n, width, device=dev)
+        us = timed(lambda: lk.experts_route(x, router, bias, top, chosen, weight))
+        record("experts_route", case, us, bytes_=n * width * 2 + E * width * 4,
+               flops=2 * n * E * width, like="linear")
+        us = timed(lambda: lk.experts_group(chosen, E, pair_of, tile_expert, slot_of, seg))
+        record("experts_group", case, us, bytes_=n * top * 12 + tiles * seg * 4)
+        used = int((tile_expert >= 0).sum())
+        weights_read = min(E, n * top) * eff * width * 2
+        if tensor:
+            us = timed(lambda: lk.experts_gather(x, pair_of, top, rows_))
+            record("experts_gather", case, us, bytes_=n * top * width * 4)
+            us = timed(lambda: lk.experts_product(rows_, up, pair_of, tile_expert, inner, False,
+                                                  "gelu_erf", ctx.status))
+            record("experts up (tensor cores)", case, us,
+                   bytes_=weights_read + n * top * (width + eff) * 2,
+                   tensor_flops=2 * n * top * width * eff, like="linear_gated")
+            us = timed(lambda: lk.experts_product(inner, down, pair_of, tile_expert, y, True, None,
+                                                  ctx.status))
+            record("experts down (tensor cores)", case, us,
+                   bytes_=weights_read + n * top * (width + eff) * 2,
+                   tensor_flops=2 * n * top * width * eff, like="linear")
+        else:
+            us = timed(lambda: lk.experts_up(x, up, pair_of, tile_expert, top, inner, "gelu_erf"))
+            record("experts up (CUDA cores)", case, us,
+                   bytes_=weights_read + n * top * (width + eff) * 2,
+                   flops=2 * used * seg * width * eff, like="linear_gated")
+            us = timed(lambda: lk.experts_down(inner, down, pair_of, tile_expert, y))
+            record("experts down (CUDA cores)", case, us,
+                   bytes_=weights_read + n * top * (width + eff) * 2,
+                   flops=2 * used * seg * width * eff, like="linear")
+        us = timed(lambda: lk.experts_combine(y, weight, eo))
+        record("experts_combine", case, us, bytes_=n * width * (top * 2 + 4), like="residual_add")
+        # the like kernels: the dense gated feed-forward of the other models
+        w_gu, w_d = w(2 * ff, width), w(width, ff)
+        act = torch.empty(n, ff, dtype=bf16, device=dev)
+        yd = torch.empty(n, width, dtype=bf16, device=dev)
+        us = timed(lambda: ops.linear_gated(x, w_gu, act, status=ctx.status))
+        record("linear_gated (other models)", case, us,
+               bytes_=(2 * ff * width + n * (width + ff)) * 2, tensor_flops=4 * n * width * ff)
+        us = timed(lambda: ops.linear(act, w_d, out=yd))
+        record("linear, down (other models)", case, us,
+               bytes_=(ff * width + n * (width + ff)) * 2, tensor_flops=2 * n * width * ff)
+        # ---- the token's side input
+        table_rows = torch.randn(MODEL["vocab_size"], side, device=dev).to(bf16)
+        ids = torch.randint(0, MODEL["vocab_size"], (n,), dtype=torch.int32, device=dev)
+        z = torch.randn(n, side, device=dev).to(bf16)
+        us = timed(lambda: ops.act_mul_row(z, ids, table_rows, z, "gelu_tanh"))
+        record("act_mul_row", case, us, bytes_=n * side * 6, like="silu_mul")
+        resid = torch.randn(n, width, device=dev)
+        us = timed(lambda: ops.add_normed(resid, yd, n_kv.new_ones(width), 1e-6))
+        record("add_normed", case, us, bytes_=n * width * (4 + 4 + 2), like="add_rmsnorm")
+        normed = torch.empty(n, width, dtype=bf16, device=dev)
+        us = timed(lambda: ops.add_rmsnorm(resid, yd, n_kv.new_ones(width), 1e-6, normed))
+        record("add_rmsnorm (other models)", case, us, bytes_=n * width * (4 + 4 + 2 + 2))
+    return out
+
+
+def workload_vapelix(args, warmup: int, steps: int) -> int:
+    """Vapelix beside Llama at equal width, vocabulary and number of layers (and as many active
+    feed-forward weights a token)."""
+    import numpy as np
+    import torch
+    from distengine_b200 import Engine, EngineConfig
+    peak, peak_kind = peaks()
+    layers = args.layers
+    rng = np.random.default_rng(0)
+    vocab = MODEL["vocab_size"]
+    result = {}
+    for name, folder in (("vapelix", vapelix_folder(layers)), ("llama", model_folder(layers))):
+        pages = (64 * (PROMPT + 8 + warmup + steps) + PREFILL) // PAGE + 64
+        engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
+                                             decode_batch_size=64, max_batch_tokens=PREFILL,
+                                             max_model_len=4096, use_graphs=not args.no_graphs))
+        prefill_ms, prefill_step_ms = timed_prefill(engine, PREFILL, rng, vocab, repeats=5)
+        entry = {"prefill_2048": {"ms": round(prefill_ms, 3),
+                                  "ms_with_host_prepare": round(prefill_step_ms, 3),
+                                  "tokens_per_s": round(PREFILL / prefill_ms * 1e3, 1)}}
+        for batch in (8, 64):
+            ms, launches, _, clocks = timed_decode(engine, batch, PROMPT, steps, warmup, rng, vocab)
+            entry[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4),
+                                         "tokens_per_s": round(batch / ms * 1e3, 1),
+                                         "gpu_launches": int(launches), "clocks": clocks}
+        result[name] = entry
+        del engine
+        torch.cuda.empty_cache()
+    mine = result["vapelix"]["decode_b8"]
+    print(json.dumps({
+        "metric": "decode tokens/s at batch 8, Vapelix at the TinyLlama-1.1B width",
+        "value": mine["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": mine["ms_per_step"], "dtype": "bf16",
+        "higher_is_better": True, "data": "synthetic", "impl": "ours", "workload": "vapelix",
+        "config": {"layers": layers, "width": MODEL["hidden_size"],
+                   "ff": MODEL["intermediate_size"], "vocab": vocab, "seq_len": PROMPT,
+                   "page_size": PAGE, "peaks": peak_kind, "shape": vapelix_shape(2)["layers"],
+                   "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed"},
+        "gpu_launches": mine["gpu_launches"], "clocks": mine["clocks"],
+        "models": result, "kernels": [] if args.only == "decode" else vapelix_kernels(peak)}))
+    return 0
+
+
 def workload_long(args, warmup: int, steps: int) -> int:
     """Llama-3-8B layer sizes: 64 requests with prompts of 4,096 tokens (fed as portions of 4,096
     tokens), then decode steps at batch 64 over the long cache; vocabulary 128,256."""
@@ -1014,9 +1300,10 @@ def main() -> int:
                         help="print one decode step's in-kernel timeline (kernels built with "
                              "DISTENGINE_B200_DEFINES=DE_TRACE)")
     parser.add_argument("--workload", default="headline",
-                        choices=["headline", "mixed", "long", "fp32", "vomotar", "sebilorn"])
+                        choices=["headline", "mixed", "long", "fp32", "vomotar", "sebilorn",
+                                 "vapelix"])
     args = parser.parse_args()
-    if (args.workload in ("mixed", "long", "vomotar", "sebilorn")
+    if (args.workload in ("mixed", "long", "vomotar", "sebilorn", "vapelix")
             and "--layers" not in " ".join(sys.argv)):
         args.layers = 8          # of the 32 that the Llama-2-7B and Llama-3-8B shapes have
 
@@ -1031,7 +1318,8 @@ def main() -> int:
     if args.workload != "headline":
         return {"mixed": workload_mixed, "long": workload_long, "fp32": workload_fp32,
                 "vomotar": workload_vomotar,
-                "sebilorn": workload_sebilorn}[args.workload](args, warmup, steps)
+                "sebilorn": workload_sebilorn,
+                "vapelix": workload_vapelix}[args.workload](args, warmup, steps)
 
     import numpy as np
     import torch

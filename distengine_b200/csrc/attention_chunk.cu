@@ -32,7 +32,8 @@ namespace {
 
 constexpr int ROWS = 8;
 constexpr int TILE = 32;
-constexpr int MAX_D = 256;
+constexpr int MAX_D = 256;        // of a value: the weighted sums live in registers
+constexpr int MAX_DK = 576;       // of a key: shared memory only
 
 struct WorkItem {
     int seq, row0, kv_begin, kv_end, partial, pad0, pad1, pad2;
@@ -1168,7 +1169,13 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
 // kernel that gives a warp four rows
 static bool vec_ok(int dtype, int dk, int dv) {
     const int pn = dtype == DE_BF16 ? 8 : 4;
-    return dk % pn == 0 && dv % pn == 0 && dk <= MAX_D && dv <= MAX_D;
+    return dk % pn == 0 && dv % pn == 0 && dk <= MAX_DK && dv <= MAX_D;
+}
+// the kernel that gives a warp one or four rows holds a tile's 16-byte pieces in at most 16
+// registers a thread
+static bool vec_fits(int dtype, int dk, int dv) {
+    const int pn = dtype == DE_BF16 ? 8 : 4;
+    return vec_ok(dtype, dk, dv) && TILE * (dk / pn + dv / pn) <= 16 * ROWS * 32;
 }
 static size_t tiled_smem(int dk, int dv) {
     return (size_t)(TILE * (dk + 4) + TILE * dv + TROWS * (dk + 4) + 4 * TILE * 16 + TILE) *
@@ -1179,7 +1186,7 @@ static size_t tiled_smem(int dk, int dv) {
 DE_EXPORT int de_attn_chunk_rows(int dtype, int dk, int dv, int wide) {
     if (!(vec_ok(dtype, dk, dv) && wide)) return ROWS;
     if (wide >= 48 && tiled_smem(dk, dv) <= 200 * 1024) return TROWS;
-    return ROWS * 4;
+    return vec_fits(dtype, dk, dv) ? ROWS * 4 : ROWS;
 }
 
 static size_t decode_smem(int dtype, int rw, int dk, int dv) {
@@ -1317,9 +1324,10 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
     if (v_stride != 0 && (v_stride < dv || (vec_ok(dtype, dk, dv) && v_stride % (dtype == DE_BF16 ? 8 : 4))))
         return -2;
     const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv};
-    if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
+    if (dk <= 0 || dk > MAX_DK || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    if (tile_rows != ROWS && !((tile_rows == ROWS * 4 || tile_rows == TROWS) && vec_ok(dtype, dk, dv)))
+    if (tile_rows != ROWS && !((tile_rows == ROWS * 4 && vec_fits(dtype, dk, dv)) ||
+                               (tile_rows == TROWS && vec_ok(dtype, dk, dv))))
         return -5;
     if (tile_rows == TROWS) {
         if ((uintptr_t)k_pages % 16 != 0 || (uintptr_t)v_pages % 16 != 0) return -5;
@@ -1353,7 +1361,7 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
 #undef TILED_N
 #undef TILED
     }
-    if (vec_ok(dtype, dk, dv) && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0) {
+    if (vec_fits(dtype, dk, dv) && (uintptr_t)k_pages % 16 == 0 && (uintptr_t)v_pages % 16 == 0) {
         const int rw = tile_rows / ROWS;
         const int pn = dtype == DE_BF16 ? 8 : 4;
         const int pieces = TILE * (dk / pn + dv / pn);

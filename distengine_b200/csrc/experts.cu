@@ -73,8 +73,9 @@ __global__ void route_kernel(const T* __restrict__ h, int ldh, const float* __re
 }
 
 // One block.  pair_of [slots] (slots = tiles * SEG), tile_expert [tiles], slot_of [pairs].
+// `seg`: the slots of a tile (a segment of an expert starts at a multiple of it).
 __global__ void group_kernel(const int* __restrict__ chosen, int pairs, int experts, int tiles,
-                             int* __restrict__ pair_of, int* __restrict__ tile_expert,
+                             int seg, int* __restrict__ pair_of, int* __restrict__ tile_expert,
                              int* __restrict__ slot_of) {
     extern __shared__ int sh[];                      // [experts] counts, then [experts] cursors
     int* count = sh;
@@ -83,7 +84,7 @@ __global__ void group_kernel(const int* __restrict__ chosen, int pairs, int expe
     pdl_trigger();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) count[e] = 0;
     for (int t = threadIdx.x; t < tiles; t += blockDim.x) tile_expert[t] = -1;
-    for (int i = threadIdx.x; i < tiles * SEG; i += blockDim.x) pair_of[i] = -1;
+    for (int i = threadIdx.x; i < tiles * seg; i += blockDim.x) pair_of[i] = -1;
     __syncthreads();
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
         const int e = chosen[p];
@@ -94,9 +95,9 @@ __global__ void group_kernel(const int* __restrict__ chosen, int pairs, int expe
         int at = 0;
         for (int e = 0; e < experts; ++e) {
             cursor[e] = at;
-            const int t = (count[e] + SEG - 1) / SEG;
-            for (int i = 0; i < t; ++i) tile_expert[at / SEG + i] = e;
-            at += t * SEG;
+            const int t = (count[e] + seg - 1) / seg;
+            for (int i = 0; i < t; ++i) tile_expert[at / seg + i] = e;
+            at += t * seg;
         }
     }
     __syncthreads();
@@ -181,6 +182,28 @@ expert_down_kernel(const T* __restrict__ inner, const T* __restrict__ down,
     }
 }
 
+// One block a slot.
+template <typename T>
+__global__ void gather_kernel(const T* __restrict__ h, int ldh, const int* __restrict__ pair_of,
+                              int top, int width, T* __restrict__ rows) {
+    pdl_wait();
+    pdl_trigger();
+    const int pair = pair_of[blockIdx.x];
+    T* dst = rows + (size_t)blockIdx.x * width;
+    const T* src = pair >= 0 ? h + (size_t)(pair / top) * ldh : nullptr;
+    constexpr int PER = 16 / sizeof(T);
+    const bool vec = width % PER == 0 && ((uintptr_t)rows % 16) == 0 &&
+                     (src == nullptr || ((uintptr_t)src % 16) == 0);
+    if (vec) {
+        for (int i = threadIdx.x; i < width / PER; i += blockDim.x)
+            reinterpret_cast<uint4*>(dst)[i] =
+                src ? reinterpret_cast<const uint4*>(src)[i] : make_uint4(0, 0, 0, 0);
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x)
+            dst[i] = src ? src[i] : from_float<T>(0.0f);
+    }
+}
+
 template <typename T>
 __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict__ weight, int top,
                                int width, size_t total, float* __restrict__ out) {
@@ -199,10 +222,10 @@ __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict_
 
 }  // namespace
 
-// How many tiles (of 64 slots) the grouped pairs of n tokens can take at most.
-DE_EXPORT int de_experts_tiles(int n, int top, int experts) {
+// How many tiles (of `seg` slots) the grouped pairs of n tokens can take at most.
+DE_EXPORT int de_experts_tiles(int n, int top, int experts, int seg) {
     const long long pairs = (long long)n * top;
-    const long long most = pairs / SEG + (experts < pairs ? experts : pairs);
+    const long long most = pairs / seg + (experts < pairs ? experts : pairs);
     return (int)(most < 1 ? 1 : most);
 }
 
@@ -223,13 +246,26 @@ DE_EXPORT int de_experts_route(int dtype, const void* h, int ldh, const float* w
                      bias, n, width, experts, top, chosen, weight);
 }
 
-DE_EXPORT int de_experts_group(const int* chosen, int pairs, int experts, int tiles, int* pair_of,
-                               int* tile_expert, int* slot_of, void* stream) {
+DE_EXPORT int de_experts_group(const int* chosen, int pairs, int experts, int tiles, int seg,
+                               int* pair_of, int* tile_expert, int* slot_of, void* stream) {
     if (pairs <= 0) return 0;
-    if (experts > 4096) return -2;
+    if (experts > 4096 || seg <= 0) return -2;
     return de_launch(group_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int),
-                     (cudaStream_t)stream, chosen, pairs, experts, tiles, pair_of, tile_expert,
-                     slot_of);
+                     (cudaStream_t)stream, chosen, pairs, experts, tiles, seg, pair_of,
+                     tile_expert, slot_of);
+}
+
+// rows[slot] = h[token of the slot's pair] (zeros for a slot without a pair): the operand of the
+// tensor-core product, whose tiles are rows of one expert.
+DE_EXPORT int de_experts_gather(int dtype, const void* h, int ldh, const int* pair_of, int slots,
+                                int top, int width, void* rows, void* stream) {
+    if (slots <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(gather_kernel<__nv_bfloat16>, dim3(slots), dim3(128), 0, s,
+                         (const __nv_bfloat16*)h, ldh, pair_of, top, width, (__nv_bfloat16*)rows);
+    return de_launch(gather_kernel<float>, dim3(slots), dim3(128), 0, s, (const float*)h, ldh,
+                     pair_of, top, width, (float*)rows);
 }
 
 DE_EXPORT int de_experts_up(int dtype, const void* h, int ldh, const void* up, const int* pair_of,

@@ -18,6 +18,13 @@
 // Tiles are numbered with the rows of x fastest, so the blocks at work share a few tiles of w.
 // No cluster launch; every block fetches its own tiles.
 //
+// Grouped form (routed experts): the rows of x are slots sorted by expert, 128 slots a tile of one
+// expert (`tile_expert`, -1: a tile without an expert, which every role skips), w is the experts'
+// matrices stacked ([experts * n_out, k]) and a tile takes its rows of w from its expert's part.
+// `pair_of` tells which slots are taken (others are not stored) and, scattering, the output row of
+// a slot.  An activation (by number, -1: none) is applied to the outputs, which are rounded to
+// bfloat16 first as a product kernel followed by an activation kernel would.
+//
 // Every wait on an mbarrier is bounded: after SPIN_LIMIT polls a thread records status 3, stops
 // waiting, and the block runs to its end (tensor memory is freed on every path); the host raises.
 //
@@ -48,7 +55,7 @@ using namespace tc5;
 // outputs, bn/2 .. bn-1 the up outputs of the same features; bn/2 columns of silu(gate) * up go out.
 template <bool GATED, typename OutT>
 __device__ __forceinline__ void store_tile(unsigned lane_base, int bn, OutT* out_row, bool row_live,
-                                           int cols_left, bool vec) {
+                                           int cols_left, bool vec, int act = -1) {
     if (GATED) {
 #pragma unroll 1
         for (int c = 0; c < bn / 2; c += 32) {
@@ -90,6 +97,11 @@ __device__ __forceinline__ void store_tile(unsigned lane_base, int bn, OutT* out
                 float y[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) y[j] = __uint_as_float(v[i + j]);
+                if (act >= 0) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        y[j] = de_activate(__bfloat162float(__float2bfloat16_rn(y[j])), act);
+                }
                 const int col = c + i;
                 if (vec && col + 8 <= cols_left) {
                     store8(out_row + col, y);
@@ -104,13 +116,16 @@ __device__ __forceinline__ void store_tile(unsigned lane_base, int bn, OutT* out
 }
 
 // map_w: the rows of w (GATED: the gate rows); map_up: the up rows (GATED only).
-template <bool GATED, typename OutT>
+// GROUPED: see the head of this file; tile_expert [tiles_m], pair_of [m_rows], scatter: a slot's
+// output row is its pair.
+template <bool GATED, typename OutT, bool GROUPED = false>
 __global__ void __launch_bounds__(THREADS, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                     const __grid_constant__ CUtensorMap map_w,
                     const __grid_constant__ CUtensorMap map_up, OutT* __restrict__ out, int ldo,
                     int m_rows, int n_out, int k_dim, int bn, int tiles_m, int tiles_n,
-                    int* status) {
+                    int* status, const int* __restrict__ tile_expert,
+                    const int* __restrict__ pair_of, int scatter, int act) {
     const int b_bytes = bn * BK * 2;
     const int out_cols = GATED ? bn / 2 : bn;             // output columns of a tile
     constexpr unsigned TMEM_COLS = 2 * MAX_BN;            // two accumulators
@@ -153,6 +168,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             int it = 0;
             for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
                 const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+                int w_row0 = tile_n * bn;
+                if (GROUPED) {
+                    const int e = tile_expert[tile_m];
+                    if (e < 0) continue;
+                    w_row0 += e * n_out;
+                }
                 for (int ks = 0; ks < k_steps; ++ks, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES) ok = mbar_wait(&empty_bar[s], ((it / STAGES) - 1) & 1, status);
@@ -166,17 +187,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
                         tma_load_2d(b_tile + b_bytes / 2, &map_up, &full_bar[s], ks * BK,
                                     tile_n * (bn / 2));
                     } else {
-                        tma_load_2d(b_tile, &map_w, &full_bar[s], ks * BK, tile_n * bn);
+                        tma_load_2d(b_tile, &map_w, &full_bar[s], ks * BK, w_row0);
                     }
                 }
             }
         }
     } else if (warp == 1) {
         // ---- tensor core: four K = 16 steps per stage, accumulators in tensor memory
+        if (GROUPED) pdl_wait();                           // tile_expert is a kernel's output
         if (lane == 0) {
             const unsigned idesc = instr_desc(BM, bn);
-            int it = 0, local = 0;
-            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+            int it = 0, local = -1;
+            for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
+                if (GROUPED && tile_expert[tile % tiles_m] < 0) continue;
+                ++local;
                 const int buf = local & 1;
                 // the epilogue has read this accumulator's tile before last
                 if (local >= 2) ok = mbar_wait(&acc_empty[buf], ((local >> 1) - 1) & 1, status);
@@ -203,18 +227,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
         // ---- epilogue: warp w reads the lanes 32 (w % 4) .. + 31 of the accumulator
         const int quarter = warp & 3;
         const bool vec = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
-        int local = 0;
-        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x, ++local) {
+        int local = -1;
+        if (GROUPED) pdl_wait();                           // tile_expert, pair_of: kernels' outputs
+        for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
             const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+            if (GROUPED && tile_expert[tile_m] < 0) continue;
+            ++local;
             const int buf = local & 1;
             ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, status);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int row = tile_m * BM + quarter * 32 + lane;
             const unsigned lane_base = tmem_base + buf * MAX_BN + ((unsigned)(quarter * 32) << 16);
-            OutT* out_row = out + (size_t)row * ldo + (size_t)tile_n * out_cols;
-            store_tile<GATED, OutT>(lane_base, bn, out_row, row < m_rows,
-                                    n_out - tile_n * out_cols, vec);
+            bool live = row < m_rows;
+            int dest = row;
+            if (GROUPED && live) {
+                const int pair = pair_of[row];
+                live = pair >= 0;
+                if (scatter) dest = pair;
+            }
+            OutT* out_row = out + (size_t)(live ? dest : 0) * ldo + (size_t)tile_n * out_cols;
+            store_tile<GATED, OutT>(lane_base, bn, out_row, live, n_out - tile_n * out_cols, vec,
+                                    GROUPED ? act : -1);
             asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);
@@ -284,7 +318,7 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, i
     code = make_map(&map_up, up, n_out, k_dim, ldw, GATED ? bn / 2 : bn);
     if (code) return code;
     const size_t smem = (size_t)SMEM_TILES + 1024;
-    auto kernel = gemm_tcgen05_kernel<GATED, OutT>;
+    auto kernel = gemm_tcgen05_kernel<GATED, OutT, false>;
     static bool sized = false;                 // per instantiation: the attribute is set once
     if (!sized) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -297,7 +331,8 @@ int launch(const void* x, int ldx, const void* w, int ldw, void* out, int ldo, i
     const int total = tiles_m * tiles_n;
     const int grid = total < sm_count() ? total : sm_count();
     return de_launch(kernel, dim3(grid), dim3(THREADS), smem, s, map_x, map_w, map_up, (OutT*)out,
-                     ldo, m_rows, n_out, k_dim, bn, tiles_m, tiles_n, status);
+                     ldo, m_rows, n_out, k_dim, bn, tiles_m, tiles_n, status, (const int*)nullptr,
+                     (const int*)nullptr, 0, -1);
 }
 
 }  // namespace
@@ -327,4 +362,39 @@ DE_EXPORT int de_gemm_tcgen05(const void* x, int ldx, const void* w, int ldw, vo
     if (out_f32)
         return launch<false, float>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, status, s);
     return launch<false, __nv_bfloat16>(x, ldx, w, ldw, out, ldo, m_rows, n_out, k_dim, status, s);
+}
+
+// The grouped product of the routed experts (see the head of this file): x [tiles * 128, k] rows
+// of slots, w [experts * n_out, k] the experts' matrices stacked, tile_expert [tiles], pair_of
+// [tiles * 128].  scatter = 0: out [tiles * 128, n_out] by slot; 1: out [pairs, n_out] by pair.
+// act: an activation's number or -1.  bfloat16 in and out.
+DE_EXPORT int de_gemm_tcgen05_grouped(const void* x, int ldx, const void* w, void* out, int ldo,
+                                      const int* tile_expert, const int* pair_of, int tiles,
+                                      int experts, int n_out, int k_dim, int scatter, int act,
+                                      int* status, void* stream) {
+    if (tiles <= 0 || n_out <= 0 || experts <= 0) return 0;
+    if (k_dim <= 0 || k_dim % 8 != 0 || ldx % 8 != 0 || ((uintptr_t)x & 15) || ((uintptr_t)w & 15))
+        return -3;
+    const int m_rows = tiles * BM;
+    const int bn = choose_bn(m_rows, n_out, false);
+    CUtensorMap map_x, map_w;
+    int code = make_map(&map_x, x, m_rows, k_dim, ldx, BM);
+    if (code) return code;
+    code = make_map(&map_w, w, experts * n_out, k_dim, k_dim, bn);
+    if (code) return code;
+    const size_t smem = (size_t)SMEM_TILES + 1024;
+    auto kernel = gemm_tcgen05_kernel<false, __nv_bfloat16, true>;
+    static bool sized = false;
+    if (!sized) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        sized = true;
+    }
+    const int tiles_n = (n_out + bn - 1) / bn;
+    const int total = tiles * tiles_n;
+    const int grid = total < sm_count() ? total : sm_count();
+    return de_launch(kernel, dim3(grid), dim3(THREADS), smem, (cudaStream_t)stream, map_x, map_w,
+                     map_w, (__nv_bfloat16*)out, ldo, m_rows, n_out, k_dim, bn, tiles, tiles_n,
+                     status, tile_expert, pair_of, scatter, act);
 }

@@ -62,9 +62,13 @@ def heads_product(a: torch.Tensor, a_head: int, w: torch.Tensor, out: torch.Tens
 
 
 # ------------------------------------------------------------------------------- routed experts
-def experts_tiles(n: int, top: int, experts: int) -> int:
-    """The most tiles of 64 slots that the grouped (token, choice) pairs of n tokens take."""
-    return int(library.load("experts").de_experts_tiles(n, top, experts))
+SEGMENT, SEGMENT_TENSOR = 64, 128      # slots of a tile: CUDA-core products, tensor-core products
+
+
+def experts_tiles(n: int, top: int, experts: int, segment: int = SEGMENT) -> int:
+    """The most tiles of ``segment`` slots that the grouped (token, choice) pairs of n tokens
+    take."""
+    return int(library.load("experts").de_experts_tiles(n, top, experts, segment))
 
 
 def experts_route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top: int,
@@ -84,17 +88,18 @@ def experts_route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top
 
 
 def experts_group(chosen: torch.Tensor, experts: int, pair_of: torch.Tensor,
-                  tile_expert: torch.Tensor, slot_of: torch.Tensor) -> None:
-    """Sort the pairs by expert: pair_of [tiles * 64] (the pair in a slot, or -1), tile_expert
-    [tiles] (or -1), slot_of [pairs]."""
+                  tile_expert: torch.Tensor, slot_of: torch.Tensor,
+                  segment: int = SEGMENT) -> None:
+    """Sort the pairs by expert: pair_of [tiles * segment] (the pair in a slot, or -1),
+    tile_expert [tiles] (or -1), slot_of [pairs]."""
     for t, name in ((chosen, "chosen"), (pair_of, "pair_of"), (tile_expert, "tile_expert"),
                     (slot_of, "slot_of")):
         _i32(t, name)
     tiles = tile_expert.shape[0]
-    _need(pair_of.shape == (tiles * 64,) and slot_of.numel() == chosen.numel(),
-          "experts_group: pair_of [tiles * 64], slot_of [pairs]")
+    _need(pair_of.shape == (tiles * segment,) and slot_of.numel() == chosen.numel(),
+          "experts_group: pair_of [tiles * segment], slot_of [pairs]")
     lib = library.load("experts")
-    _check(lib.de_experts_group(chosen.data_ptr(), chosen.numel(), experts, tiles,
+    _check(lib.de_experts_group(chosen.data_ptr(), chosen.numel(), experts, tiles, segment,
                                 pair_of.data_ptr(), tile_expert.data_ptr(), slot_of.data_ptr(),
                                 _stream()), "experts_group")
 
@@ -125,6 +130,50 @@ def experts_down(inner: torch.Tensor, down: torch.Tensor, pair_of: torch.Tensor,
     _check(lib.de_experts_down(_tag(inner.dtype), inner.data_ptr(), down.data_ptr(),
                                pair_of.data_ptr(), tile_expert.data_ptr(), tiles, width, ff,
                                y.data_ptr(), _stream()), "experts_down")
+
+
+def experts_tensor_ok(h: torch.Tensor, up: torch.Tensor, pairs: int) -> bool:
+    """Whether the experts' products of this step go to the tensor cores (``experts_product``):
+    bfloat16, rows of whole 16-byte pieces, and enough pairs that tiles of 128 slots are worth
+    their padding."""
+    return (h.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and pairs >= TENSOR_PAIRS
+            and up.shape[1] % 8 == 0 and up.shape[2] % 8 == 0)
+
+
+TENSOR_PAIRS = 512
+
+
+def experts_gather(h: torch.Tensor, pair_of: torch.Tensor, top: int, rows: torch.Tensor) -> None:
+    """rows[slot] = h[token of the slot's pair], zeros for a slot without a pair."""
+    _i32(pair_of, "pair_of")
+    _need(h.stride(1) == 1 and rows.is_contiguous() and rows.dtype == h.dtype
+          and rows.shape == (pair_of.shape[0], h.shape[1]), "experts_gather: rows [slots, D]")
+    lib = library.load("experts")
+    _check(lib.de_experts_gather(_tag(h.dtype), h.data_ptr(), h.stride(0), pair_of.data_ptr(),
+                                 pair_of.shape[0], top, h.shape[1], rows.data_ptr(), _stream()),
+           "experts_gather")
+
+
+def experts_product(rows: torch.Tensor, w: torch.Tensor, pair_of: torch.Tensor,
+                    tile_expert: torch.Tensor, out: torch.Tensor, scatter: bool,
+                    act: "str | None", status: torch.Tensor) -> None:
+    """The experts' products on the 5th-generation tensor cores (the grouped form of
+    ``csrc/gemm_tcgen05.cu``): rows [tiles * 128, k] slots sorted by expert, w [E, n, k];
+    out[slot] (``scatter``: out[pair of the slot]) = act(w[expert of the slot's tile] rows[slot])
+    for the slots that hold a pair.  bfloat16."""
+    experts, n_out, k = w.shape
+    tiles = tile_expert.shape[0]
+    _need(rows.dtype == w.dtype == out.dtype == torch.bfloat16 and rows.is_contiguous()
+          and w.is_contiguous() and out.is_contiguous() and rows.shape == (tiles * 128, k)
+          and pair_of.shape == (tiles * 128,) and out.shape[1] == n_out
+          and (scatter or out.shape[0] == tiles * 128) and (act is None or act in ACTIVATIONS),
+          "experts_product: rows [tiles * 128, k], w [E, n, k], out [.., n], bfloat16")
+    lib = library.load("gemm_tcgen05")
+    _check(lib.de_gemm_tcgen05_grouped(rows.data_ptr(), rows.stride(0), w.data_ptr(),
+                                       out.data_ptr(), out.stride(0), tile_expert.data_ptr(),
+                                       pair_of.data_ptr(), tiles, experts, n_out, k,
+                                       1 if scatter else 0, -1 if act is None else ACTIVATIONS[act],
+                                       status.data_ptr(), _stream()), "experts_product")
 
 
 def experts_combine(y: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:

@@ -61,6 +61,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
     "gemm_tcgen05": {
         "de_gemm_tcgen05": [P, I, P, I, P, I, I, I, I, I, I, P, P],
         "de_gemm_tcgen05_tile": [I, I, I], "de_gemm_tcgen05_sms": [],
+        "de_gemm_tcgen05_grouped": [P, I, P, P, I, P, P, I, I, I, I, I, I, P, P],
     },
     "attention_tcgen05": {
         "de_attn_tcgen05_rows": [], "de_attn_tcgen05_head_dim": [],
@@ -101,9 +102,10 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_heads_product": [I, I, I, P, I, I, P, P, I, I, P, I, I, I, I, I, P],
     },
     "experts": {
-        "de_experts_tiles": [I, I, I],
+        "de_experts_tiles": [I, I, I, I],
+        "de_experts_gather": [I, P, I, P, I, I, I, P, P],
         "de_experts_route": [I, P, I, P, P, I, I, I, I, P, P, P],
-        "de_experts_group": [P, I, I, I, P, P, P, P],
+        "de_experts_group": [P, I, I, I, I, P, P, P, P],
         "de_experts_up": [I, P, I, P, P, P, I, I, I, I, P, I, P],
         "de_experts_down": [I, P, P, P, P, I, I, I, P, P],
         "de_experts_combine": [I, P, P, I, I, I, P, P],

@@ -6,8 +6,12 @@ layers down_e(act(up_e x)) (no gate, no biases) that a router picks.
     out = sum over the chosen e of weight_e * W_down_e act(W_up_e x)      summed in float32
 
 The experts' matrices are stacked ([E, inner, width] and [E, width, inner]); the (token, choice)
-pairs are sorted by expert on the device and every tile of 64 pairs of one expert is one block's
-product (``csrc/experts.cu``).  The output is float32: it joins the residual stream unrounded.
+pairs are sorted by expert on the device into tiles of slots of one expert each.  A step of few
+pairs, and every float32 step, runs a tile of 64 slots as one block's product on the CUDA cores
+(``csrc/experts.cu``); a bfloat16 step of many pairs gathers its rows by slot and runs tiles of
+128 slots on the tensor cores (the grouped form of ``csrc/gemm_tcgen05.cu``, the activation in
+its epilogue, the down product scattering its rows to their pairs).  The output is float32: it
+joins the residual stream unrounded.
 """
 
 from __future__ import annotations
@@ -52,22 +56,31 @@ class RoutedExperts(FeedForward):
             self.device)
 
     def kernel_modules(self):
-        return ("experts",)
+        return ("experts", "gemm_tcgen05") if self.dtype == torch.bfloat16 else ("experts",)
 
     def forward(self, x: torch.Tensor, ctx: StepContext, ahead=None) -> torch.Tensor:
         n, top = x.shape[0], self.top
-        tiles = lk.experts_tiles(n, top, self.experts)
+        tensor = lk.experts_tensor_ok(x, self.up, n * top)
+        segment = lk.SEGMENT_TENSOR if tensor else lk.SEGMENT
+        tiles = lk.experts_tiles(n, top, self.experts, segment)
         chosen = ctx.buffer("experts.chosen", (n, top), torch.int32)
         weight = ctx.buffer("experts.weight", (n, top), torch.float32)
-        pair_of = ctx.buffer("experts.pair_of", (tiles * 64,), torch.int32)
+        pair_of = ctx.buffer("experts.pair_of", (tiles * segment,), torch.int32)
         tile_expert = ctx.buffer("experts.tile_expert", (tiles,), torch.int32)
         slot_of = ctx.buffer("experts.slot_of", (n * top,), torch.int32)
         lk.experts_route(x, self.router, self.bias, top, chosen, weight)
-        lk.experts_group(chosen, self.experts, pair_of, tile_expert, slot_of)
-        inner = ctx.buffer("experts.inner", (tiles * 64, self.inner))
-        lk.experts_up(x, self.up, pair_of, tile_expert, top, inner, self.activation)
+        lk.experts_group(chosen, self.experts, pair_of, tile_expert, slot_of, segment)
+        inner = ctx.buffer("experts.inner", (tiles * segment, self.inner))
         y = ctx.buffer("experts.y", (n * top, self.width))
-        lk.experts_down(inner, self.down, pair_of, tile_expert, y)
+        if tensor:
+            rows = ctx.buffer("experts.rows", (tiles * segment, self.width))
+            lk.experts_gather(x, pair_of, top, rows)
+            lk.experts_product(rows, self.up, pair_of, tile_expert, inner, False,
+                               self.activation, ctx.status)
+            lk.experts_product(inner, self.down, pair_of, tile_expert, y, True, None, ctx.status)
+        else:
+            lk.experts_up(x, self.up, pair_of, tile_expert, top, inner, self.activation)
+            lk.experts_down(inner, self.down, pair_of, tile_expert, y)
         out = ctx.buffer("experts.out", (n, self.width), torch.float32)
         lk.experts_combine(y, weight, out)
         return out

@@ -39,7 +39,8 @@ from .base import Mixer, PagedKVSpec, compute_matrix, register_mixer, stored_vec
 from .context import CacheBinding, StepContext, StepPrep
 from .recurrent import stack_segments
 
-MAX_DIM = 256                   # of kv_rank + rotary_dim: what the attention kernels take
+MAX_RANK, MAX_ROW = 256, 576    # of kv_rank and of kv_rank + rotary_dim: what the attention
+                                # kernels take as value and key sizes
 
 
 def stretched_frequencies(theta: float, dims: int, scaling=None) -> "tuple[torch.Tensor, float]":
@@ -68,8 +69,9 @@ class LatentAttention(Mixer):
         super().__init__(dtype, device)
         if rotary_dim % 2 or rotary_dim < 0:
             raise ValueError(f"latent_attention: rotary_dim ({rotary_dim}) must be even")
-        if kv_rank + rotary_dim > MAX_DIM:
-            raise ValueError(f"latent_attention: kv_rank + rotary_dim up to {MAX_DIM}, got "
+        if kv_rank > MAX_RANK or kv_rank + rotary_dim > MAX_ROW:
+            raise ValueError(f"latent_attention: kv_rank up to {MAX_RANK} and kv_rank + "
+                             f"rotary_dim up to {MAX_ROW}, got {kv_rank} and "
                              f"{kv_rank + rotary_dim}")
         self.width, self.heads, self.dim, self.rot, self.dv = width, heads, key_dim, rotary_dim, value_dim
         self.q_rank, self.rank, self.scale, self.eps = q_rank, kv_rank, float(scale), float(eps)

@@ -187,10 +187,13 @@ class PartHarness:
                                   poison_freed_pages=True)
         self.runner = StepRunner(self.model, self.cache)
 
-    def run(self, entries, fn):
-        """entries: list of (request id, number of new tokens)."""
+    def run(self, entries, fn, tokens=None):
+        """entries: list of (request id, number of new tokens); ``tokens``: request id -> the
+        token ids of this step (zeros without)."""
         from distengine_b200.engine.step import StepEntry
         self.model.fn = fn
-        out = self.runner.step([StepEntry(rid, [0] * n, []) for rid, n in entries])
+        tokens = tokens or {}
+        out = self.runner.step([StepEntry(rid, list(tokens.get(rid, [0] * n)), [])
+                                for rid, n in entries])
         self.runner.check_status()
         return out

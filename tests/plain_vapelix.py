@@ -120,9 +120,25 @@ def route(h, w, prefix, top):
     return chosen, torch.softmax(best, dim=-1)
 
 
-def routed_feed_forward(h, w, prefix, experts, top, act=None):
-    """sum over the chosen experts e of weight_e * W_down_e gelu_erf(W_up_e h)."""
-    chosen, weights = route(h, w, prefix, top)
+def routed_feed_forward(h, w, prefix, experts, top, act=None, chosen=None, slack=None):
+    """sum over the chosen experts e of weight_e * W_down_e gelu_erf(W_up_e h).
+
+    ``chosen`` [T, top] takes the place of the router's choice (an implementation in bfloat16 sees
+    slightly different logits, and where two are nearly tied it may pick the other): the weights
+    are then the softmax over the logits of those experts, and ``slack`` (a list) receives by how
+    much the smallest of them lies below the ``top``-th largest logit, as a share of the logits'
+    spread, which is 0 where the choice is the router's."""
+    if chosen is None:
+        chosen, weights = route(h, w, prefix, top)
+    else:
+        z = h @ w[prefix + "router"].to(h.dtype).t() + w[prefix + "router.b"].to(h.dtype)
+        mine = torch.gather(z, 1, chosen.long())
+        assert all(len(set(row)) == top for row in chosen.tolist()), "an expert chosen twice"
+        weights = torch.softmax(mine, dim=-1)
+        if slack is not None:
+            kth = torch.topk(z, top, dim=-1).values[:, -1]
+            spread = (z.max(dim=-1).values - z.min(dim=-1).values).clamp_min(1e-9)
+            slack.append(float(((kth - mine.min(dim=-1).values) / spread).max()))
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, weight in zip(chosen[t].tolist(), weights[t]):
@@ -154,8 +170,9 @@ def run_order(config) -> list[tuple[int, bool]]:
     return order + [(i, False) for i in range(stop, n)]
 
 
-def layer(x, tokens, w, config, index, act=None):
-    """x + mixer(norm1 x) + ff(norm2 x), both branches of the same x; then the token's side input."""
+def layer(x, tokens, w, config, index, act=None, chosen=None, slack=None):
+    """x + mixer(norm1 x) + ff(norm2 x), both branches of the same x; then the token's side input.
+    ``chosen``, ``slack``: see ``routed_feed_forward``."""
     entry, eps, prefix = config["layers"][index], config["norm"]["eps"], f"l{index}."
     h = rms_norm(x, w[prefix + "norm1"], eps, act)
     branch = latent_attention(h, w, prefix + "mix.", entry["mixer"], eps, act=act)
@@ -166,7 +183,7 @@ def layer(x, tokens, w, config, index, act=None):
             branch = branch + gated_feed_forward(h2, w, prefix + "mlp.", act)
         else:
             branch = branch + routed_feed_forward(h2, w, prefix + "mlp.", mlp["router"]["experts"],
-                                                  mlp["router"]["top"], act)
+                                                  mlp["router"]["top"], act, chosen, slack)
     x = x + branch
     side = config.get("token_side")
     if side:
@@ -174,17 +191,20 @@ def layer(x, tokens, w, config, index, act=None):
     return x
 
 
-def forward(tokens, w, config, act=None, dtype=torch.float64, trace=None):
+def forward(tokens, w, config, act=None, dtype=torch.float64, trace=None, routing=None,
+            slack=None):
     """Logits [T, vocab] of one whole sequence.  ``trace``: a list that receives the residual
-    stream after every layer run."""
+    stream after every layer run.  ``routing``: layer run -> chosen experts [T, top], in place of
+    the router's choice in that run (see ``routed_feed_forward``, also for ``slack``)."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     first = w["embed"][tokens]
     x = first.clone()
-    for index, add_first in run_order(config):
+    for run, (index, add_first) in enumerate(run_order(config)):
         if add_first:
             x = x + first
-        x = layer(x, tokens, w, config, index, act)
+        x = layer(x, tokens, w, config, index, act, None if routing is None else routing.get(run),
+                  slack)
         if trace is not None:
             trace.append(x.clone())
     last = rms_norm(x, w["final.norm"], config["norm"]["eps"], act)
