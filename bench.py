@@ -940,7 +940,7 @@ def vapelix_kernels(peak: dict) -> list[dict]:
                bytes_=n * H * (dim + rank) * 2 + H * rank * dim * 2, flops=2 * n * H * dim * rank,
                like="linear")
         mixed = torch.empty(n, H * rank, device=dev)
-        if n == s and rk.chunk_decode_ok(bf16, H, 1, row, rank):
+        if n == s and rk.chunk_decode_ok(bf16, H, 1, row, rank, True):
             us = timed(lambda: rk.chunk_attention_decode(folded, mixed, pages, pages, table, None,
                                                          None, H, 1, row, rank, m["scale"], 0, ctx,
                                                          v_stride=row))

@@ -905,13 +905,19 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
     float* Pacc = Pml + ROWS * RW * 2;               // [ROWS warps][RW][dv]
     // a warp's tile: key rows at a stride that keeps 16-byte reads of 8 lanes on different banks
     const int k_stride = ((dk * (int)sizeof(T) + 127) / 128) * 128 + 16;       // bytes
-    const int tile_bytes = TILE * k_stride + TILE * dv * (int)sizeof(T);
+    // values that are the first dv features of the keys (one set of pages, rows of dk) are read
+    // from the key tile
+    const bool v_in_k = v_pages == k_pages && sight.v_stride == dk;
+    const int tile_bytes = TILE * k_stride + (v_in_k ? 0 : TILE * dv * (int)sizeof(T));
     char* mine = reinterpret_cast<char*>(Pacc + ROWS * RW * dv) +
                  (size_t)(threadIdx.x >> 5) * tile_bytes;
     char* Kt = mine;
     const T* Vt = reinterpret_cast<const T*>(mine + TILE * k_stride);
-    const int seq = blockIdx.x, hk = blockIdx.y;
-    const int g = heads / kv_heads;
+    // a kv head with more than RW query heads is shared by several blocks, RW heads each
+    const int parts = gridDim.y / kv_heads;
+    const int seq = blockIdx.x, hk = blockIdx.y / parts;
+    const int h0 = hk * (heads / kv_heads) + (blockIdx.y % parts) * RW;   // the block's first head
+    const int g = min(RW, (hk + 1) * (heads / kv_heads) - h0);            // and how many it has
     const int pos = seq_pos0[seq], slot = seq_slot[seq], tok = seq_qstart[seq];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int lo = sight_lo(sight, pos), hi = pos + 1, first = sight_first(sight, lo);
@@ -924,7 +930,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
     float pen1[RW], pen2[RW], m[RW], l[RW];
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
-        const int hq = hk * g + min(i, g - 1);
+        const int hq = h0 + min(i, g - 1);
         pen1[i] = penalty ? r1[hq] : 0.0f;
         pen2[i] = penalty ? r2[hq] : 0.0f;
         m[i] = -INFINITY;
@@ -933,7 +939,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
     pdl_wait();
     for (int e = threadIdx.x; e < RW * dk; e += ROWS * 32) {
         const int i = e / dk, d = e - i * dk;
-        Qs[e] = i < g ? to_float(q[(size_t)tok * q_stride + (hk * g + i) * dk + d]) : 0.0f;
+        Qs[e] = i < g ? to_float(q[(size_t)tok * q_stride + (h0 + i) * dk + d]) : 0.0f;
     }
     __syncthreads();
     if (fuse.on) {
@@ -1017,7 +1023,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
                 const bool ok = __shfl_sync(0xffffffffu, (int)valid, j) != 0;
                 if (ok) cp_async_16(Kt + j * k_stride + w * 16, k_pages + (size_t)rj * dk + w * PN);
             }
-            for (int e = lane; e < TILE * cv; e += 32) {
+            for (int e = lane; e < (v_in_k ? 0 : TILE * cv); e += 32) {
                 const int j = e / cv, w = e - j * cv;
                 const unsigned long long rj = __shfl_sync(0xffffffffu, (unsigned long long)row, j);
                 const bool ok = __shfl_sync(0xffffffffu, (int)valid, j) != 0;
@@ -1078,7 +1084,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
                 zero &= pj[i] == 0.0f;
             }
             if (zero) continue;
-            const T* vr = Vt + (size_t)j * dv;
+            const T* vr = v_in_k ? reinterpret_cast<const T*>(Kt + j * k_stride) : Vt + (size_t)j * dv;
 #pragma unroll
             for (int b = 0; b < MAX_D / 32; ++b) {
                 const int dd = lane + 32 * b;
@@ -1122,7 +1128,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
             }
         }
         const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-        const size_t o = (size_t)tok * out_stride + (hk * g + i) * dv;
+        const size_t o = (size_t)tok * out_stride + (h0 + i) * dv;
         if (fuse.on) {
             // the head's result through shared memory (the place of the first warp's share of
             // this head, which only this warp reads), so that a lane finds its feature's pair
@@ -1136,7 +1142,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
             __syncwarp();
             const int vhalf = dv / 2;
             const T* gt = fuse.gate
-                              ? (const T*)fuse.gate + (size_t)tok * fuse.ld_gate + (hk * g + i) * dv
+                              ? (const T*)fuse.gate + (size_t)tok * fuse.ld_gate + (h0 + i) * dv
                               : nullptr;
 #pragma unroll
             for (int b = 0; b < MAX_D / 32; ++b) {
@@ -1189,20 +1195,34 @@ DE_EXPORT int de_attn_chunk_rows(int dtype, int dk, int dv, int wide) {
     return vec_fits(dtype, dk, dv) ? ROWS * 4 : ROWS;
 }
 
-static size_t decode_smem(int dtype, int rw, int dk, int dv) {
+static size_t decode_smem(int dtype, int rw, int dk, int dv, int v_in_k) {
     const int size = dtype == DE_BF16 ? 2 : 4;
-    const size_t tile = (size_t)TILE * (((dk * size + 127) / 128) * 128 + 16) + (size_t)TILE * dv * size;
+    const size_t tile = (size_t)TILE * (((dk * size + 127) / 128) * 128 + 16) +
+                        (v_in_k ? 0 : (size_t)TILE * dv * size);
     return (size_t)(rw * dk + ROWS * rw * 2 + ROWS * rw * dv) * sizeof(float) + ROWS * tile;
 }
 
-// Whether steps of single tokens go to the kernel that takes a (sequence, kv head) a block: rows
-// of whole 16-byte pieces, at most 8 query heads a kv head, and its eight tiles fit an SM.
-DE_EXPORT int de_attn_chunk_decode_ok(int dtype, int heads, int kv_heads, int dk, int dv) {
-    if (!(vec_ok(dtype, dk, dv) && kv_heads > 0 && heads % kv_heads == 0 && heads / kv_heads <= 8))
-        return 0;
+// The query heads a block of the single-token kernel takes (0: the kernel does not take this
+// shape).  Keys and values of their own: up to 8 query heads a kv head, all in one block, if the
+// eight warps' tiles then fit an SM.  Values inside the keys (`v_in_k`): any number of heads;
+// several blocks share a kv head, each with as many heads (up to 8) as fit.
+static int decode_rows(int dtype, int heads, int kv_heads, int dk, int dv, int v_in_k) {
+    if (!(vec_ok(dtype, dk, dv) && kv_heads > 0 && heads % kv_heads == 0)) return 0;
     const int g = heads / kv_heads;
-    const int rw = g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
-    return decode_smem(dtype, rw, dk, dv) <= 200 * 1024;
+    int rw = g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
+    if (!v_in_k) return g <= 8 && decode_smem(dtype, rw, dk, dv, 0) <= 200 * 1024 ? rw : 0;
+    if (decode_smem(dtype, rw, dk, dv, v_in_k) <= 200 * 1024) return rw;
+    while ((rw >>= 1) >= 1)
+        if (decode_smem(dtype, rw, dk, dv, v_in_k) <= 216 * 1024) return rw;
+    return 0;
+}
+
+// Whether steps of single tokens go to the kernel that takes a (sequence, kv head) a block, or a
+// few blocks where a kv head has many query heads: rows of whole 16-byte pieces, and its eight
+// tiles fit an SM.  v_in_k: the values are the first dv features of the keys.
+DE_EXPORT int de_attn_chunk_decode_ok(int dtype, int heads, int kv_heads, int dk, int dv,
+                                      int v_in_k) {
+    return decode_rows(dtype, heads, kv_heads, dk, dv, v_in_k) > 0;
 }
 
 DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void* out,
@@ -1222,14 +1242,15 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
     const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv};
     const Fuse fuse = {fused, fk, rot, fv, write_kv, gate, ld_gate};
     if (fused && (rot < 0 || rot % 2 || rot > dk || (fv != nullptr && dv % 2) || out_f32)) return -2;
-    if (!de_attn_chunk_decode_ok(dtype, heads, kv_heads, dk, dv) || (uintptr_t)k_pages % 16 != 0)
-        return -2;
+    const int v_in_k = v_pages == k_pages && v_stride == dk;
+    const int rw = decode_rows(dtype, heads, kv_heads, dk, dv, v_in_k);
+    if (rw == 0 || (uintptr_t)k_pages % 16 != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     const int g = heads / kv_heads;
-    const int rw = g <= 1 ? 1 : (g <= 2 ? 2 : (g <= 4 ? 4 : 8));
-    const size_t smem = decode_smem(dtype, rw, dk, dv);
+    const size_t smem = decode_smem(dtype, rw, dk, dv, v_in_k);
     if ((uintptr_t)v_pages % 16 != 0) return -2;
-    dim3 grid(n_seqs, kv_heads);
+    if (g > rw && fused) return -2;         // a kv head's blocks would each store the token's key
+    dim3 grid(n_seqs, kv_heads * ((g + rw - 1) / rw));
 #define DEC(T, RW)                                                                              \
     do {                                                                                        \
         if (smem > 48 * 1024) {                                                                 \

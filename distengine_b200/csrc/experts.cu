@@ -22,27 +22,61 @@ namespace {
 constexpr int SEG = rows_product::TILE;     // segments of an expert start at multiples of this
 constexpr int MAX_TOP = 32;
 
-// One warp a token.  logits live in shared memory, [warps][experts].
+// One block of eight warps a token.  Warp w takes the w-th eighth of the features for all experts
+// (eight experts at a time, eight chains of multiply-adds side by side); a logit is the sum of the
+// warps' shares in the order of the warps, plus the bias.  The order of the sums is fixed, so a
+// token's logits do not depend on its step.  Then warp 0 picks the `top` largest (ties: the lower
+// index) and forms the softmax over them.  Shared memory: [9][experts] floats.
+constexpr int ROUTE_WARPS = 8;
 template <typename T>
-__global__ void route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w,
-                             const float* __restrict__ bias, int n, int width, int experts,
-                             int top, int* __restrict__ chosen, float* __restrict__ weight) {
+__global__ void __launch_bounds__(ROUTE_WARPS * 32)
+route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w,
+             const float* __restrict__ bias, int n, int width, int experts, int top,
+             int* __restrict__ chosen, float* __restrict__ weight) {
     extern __shared__ float zs[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int row = blockIdx.x * (blockDim.x >> 5) + warp;
-    float* z = zs + (size_t)warp * experts;
+    const int row = blockIdx.x;
+    float* z = zs + (size_t)ROUTE_WARPS * experts;
     pdl_wait();
     pdl_trigger();
-    if (row >= n) return;
     const T* x = h + (size_t)row * ldh;
-    for (int e = 0; e < experts; ++e) {
-        const float* wr = w + (size_t)e * width;
-        float s = 0.0f;
-        for (int i = lane; i < width; i += 32) s = fmaf(to_float(x[i]), wr[i], s);
-        s = warp_sum(s);
-        if (lane == 0) z[e] = s + bias[e];
+    const int slice = ((width + ROUTE_WARPS - 1) / ROUTE_WARPS + 31) / 32 * 32;
+    const int i0 = warp * slice, i1 = min(width, i0 + slice);
+    for (int e0 = 0; e0 < experts; e0 += 8) {
+        float s[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s[u] = 0.0f;
+        const float* wr = w + (size_t)e0 * width;
+        if (e0 + 8 <= experts) {
+#pragma unroll 2
+            for (int i = i0 + lane; i < i1; i += 32) {
+                const float xv = to_float(x[i]);
+#pragma unroll
+                for (int u = 0; u < 8; ++u) s[u] = fmaf(xv, wr[(size_t)u * width + i], s[u]);
+            }
+        } else {
+            for (int i = i0 + lane; i < i1; i += 32) {
+                const float xv = to_float(x[i]);
+#pragma unroll
+                for (int u = 0; u < 8; ++u)
+                    if (e0 + u < experts) s[u] = fmaf(xv, wr[(size_t)u * width + i], s[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const float t = warp_sum(s[u]);
+            if (lane == 0 && e0 + u < experts) zs[(size_t)warp * experts + e0 + u] = t;
+        }
     }
-    __syncwarp();
+    __syncthreads();
+    for (int e = threadIdx.x; e < experts; e += ROUTE_WARPS * 32) {
+        float t = 0.0f;
+#pragma unroll
+        for (int k = 0; k < ROUTE_WARPS; ++k) t += zs[(size_t)k * experts + e];
+        z[e] = t + bias[e];
+    }
+    __syncthreads();
+    if (warp != 0) return;
     float best[MAX_TOP];
     float total = 0.0f;
     for (int k = 0; k < top; ++k) {
@@ -233,11 +267,11 @@ DE_EXPORT int de_experts_route(int dtype, const void* h, int ldh, const float* w
                                const float* bias, int n, int width, int experts, int top,
                                int* chosen, float* weight, void* stream) {
     if (n <= 0) return 0;
-    if (top <= 0 || top > MAX_TOP || top > experts || experts > 4096) return -2;
+    if (top <= 0 || top > MAX_TOP || top > experts || experts > 1024) return -2;
     cudaStream_t s = (cudaStream_t)stream;
-    const int warps = 4;
-    const size_t smem = (size_t)warps * experts * sizeof(float);
-    const dim3 grid((n + warps - 1) / warps);
+    const int warps = ROUTE_WARPS;
+    const size_t smem = (size_t)(warps + 1) * experts * sizeof(float);
+    const dim3 grid(n);
     if (dtype == DE_BF16)
         return de_launch(route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, s,
                          (const __nv_bfloat16*)h, ldh, w, bias, n, width, experts, top, chosen,

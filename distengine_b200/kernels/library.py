@@ -74,7 +74,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
     },
     "attention_chunk": {
         "de_attn_chunk_rows": [I, I, I, I],
-        "de_attn_chunk_decode_ok": [I, I, I, I, I],
+        "de_attn_chunk_decode_ok": [I, I, I, I, I, I],
         "de_attn_chunk_decode": [I, P, I, P, I, P, P, P, I, I, P, P, P, I, P, P, I, I, I, I, I, F,
                                  I, I, I, F, I, I, P, I, P, I, P, I, I, P, P],
         "de_kv_write_rotated": [I, P, I, P, P, P, I, P, I, I, I, I, P, P, P, I, I, I, I, I, P, P],

@@ -271,10 +271,11 @@ def long_portion_rows(seq_qlen, heads: int, kv_heads: int) -> int:
 
 
 def chunk_decode_ok(dtype: torch.dtype, heads: int, kv_heads: int, key_dim: int,
-                    value_dim: int) -> bool:
-    """Whether steps of single tokens can go to ``chunk_attention_decode``."""
+                    value_dim: int, values_in_keys: bool = False) -> bool:
+    """Whether steps of single tokens can go to ``chunk_attention_decode``.  ``values_in_keys``:
+    the values are the first ``value_dim`` features of the keys (one set of pages)."""
     return bool(library.load("attention_chunk").de_attn_chunk_decode_ok(
-        _tag(dtype), heads, kv_heads, key_dim, value_dim))
+        _tag(dtype), heads, kv_heads, key_dim, value_dim, 1 if values_in_keys else 0))
 
 
 def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,

@@ -74,7 +74,8 @@ class DecoderModel:
             if kind == "vector":
                 vectors.add(names["final_norm"] + local)
         expected[names["output"]] = (self.config.vocabulary, self.config.width)
-        optional = {names["output"]} if self.config.tied_output else set()
+        # a tied output needs no tensor of its own, unless it goes by the embedding's name
+        optional = ({names["output"]} - {names["embedding"]}) if self.config.tied_output else set()
         return expected, vectors, optional
 
     def kernel_modules(self) -> "list[tuple[str, tuple]]":

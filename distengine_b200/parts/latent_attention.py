@@ -115,7 +115,7 @@ class LatentAttention(Mixer):
         return self.key
 
     def _decode_kernel(self) -> bool:
-        return rk.chunk_decode_ok(self.dtype, self.heads, 1, self.row, self.rank)
+        return rk.chunk_decode_ok(self.dtype, self.heads, 1, self.row, self.rank, True)
 
     def prepare(self, prep: StepPrep) -> None:
         """The step's tiles of rows (work items of ``kernels.attention_plan``, unsplit): all heads

@@ -21,7 +21,7 @@ def test_round_trip_and_tensors(name):
     assert VapelixConfig.from_json(config.to_json()) == config
     expected, vectors, optional = expected_tensors(config)
     assert {k: tuple(v) for k, v in expected.items()} == pv.tensor_shapes(vc.ALL[name])
-    assert "final.norm" in vectors and "l0.norm1" in vectors and "embed" in optional
+    assert "final.norm" in vectors and "l0.norm1" in vectors and not optional
     assert config.tied_output
 
 
