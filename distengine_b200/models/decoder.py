@@ -87,7 +87,8 @@ class DecoderModel:
                 for module in part.kernel_modules():
                     if module not in modules:
                         modules.append(module)
-        return [(module, ()) for module in modules]
+        # a part names a library, or (library, the definitions it is built with)
+        return [module if isinstance(module, tuple) else (module, ()) for module in modules]
 
     def load(self, tensors: dict[str, torch.Tensor]) -> None:
         if self.device.type == "cuda":

@@ -21,7 +21,15 @@ lo = max(floor(d(fast)), 0), hi = min(ceil(d(slow)), rotary_dim - 1) and the ram
 r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), f_i <- f_i / factor * r_i + f_i * (1 - r_i), and
 cosines and sines are multiplied by 0.1 ln(factor) + 1.  ``scale`` is used as it is given.
 
-Scores, softmax weights, the weighted sum over the latent, angles and norm statistics are float32.
+Steps with prompt portions in bfloat16, when the cached row is a multiple of 16 features up to the
+tensor-core attention's largest head: the kernels of ``kernels.attention`` (mma.sync, or tcgen05
+at rows of 64 and 128 features) run it as one key/value head whose value pages are its key pages;
+the weighted sums then cover the whole row, and the per-head value product reads their first
+kv_rank features.  Other steps: the CUDA-core kernels of ``csrc/attention_chunk.cu``.
+
+Scores, softmax weights, angles and norm statistics are float32; so is the weighted sum over the
+latent on the CUDA-core kernels (the tensor-core kernels round the softmax weights and the sums
+to bfloat16, as they do for every model).
 """
 
 from __future__ import annotations
@@ -34,6 +42,7 @@ import torch
 from ..kernels import latent as lk
 from ..kernels import ops
 from ..kernels import recurrent as rk
+from ..kernels.attention import MAX_HEAD_DIM, AttentionLauncher, uses_tensor_cores
 from ..kernels.attention_plan import build_plan
 from .base import Mixer, PagedKVSpec, compute_matrix, register_mixer, stored_vector
 from .context import CacheBinding, StepContext, StepPrep
@@ -79,6 +88,10 @@ class LatentAttention(Mixer):
         self.freq = freq.to(device)
         self.row = kv_rank + rotary_dim              # what a key's row in the pages holds
         self.key = f"latent_attention/{heads}/{kv_rank}/{rotary_dim}"
+        # prompt portions on the tensor cores: one key/value head of `row` features
+        self.launcher = None
+        if uses_tensor_cores(dtype, self.row) and self.row <= MAX_HEAD_DIM:
+            self.launcher = AttentionLauncher(dtype, heads, 1, self.row, self.scale, None, device)
 
     def tensors(self):
         d, h = self.width, self.heads
@@ -105,7 +118,12 @@ class LatentAttention(Mixer):
         self.n_kv = stored_vector(tensors["dkv.norm"], self.dtype, self.device)
 
     def kernel_modules(self):
-        return ("attention_chunk", "latent")
+        mine = ("attention_chunk", "latent")
+        if self.launcher is None:
+            return mine
+        # the launcher's kernels for work items (not its single-token one, which is not used here)
+        wide = (self.launcher.tcgen05_module,) if self.launcher.shapes[0].code == 2 else ()
+        return mine + (self.launcher.module, ("attention_simt", ())) + wide
 
     def cache_spec(self):
         return PagedKVSpec(1, self.row, value_dim=self.rank, values_in_keys=True)
@@ -129,6 +147,11 @@ class LatentAttention(Mixer):
             prep.add(name, np.zeros((0, 8), dtype=np.int32))
             prep.notes[self.key] = 0
             return
+        if self.launcher is not None:
+            self.launcher.prepare(prep, allow_decode=False)
+            prep.add(name, np.zeros((0, 8), dtype=np.int32))
+            prep.notes[self.key] = -1
+            return
         rows = rk.chunk_rows_per_tile(self.dtype, self.row, self.rank, longest > 1,
                                       rk.long_portion_rows(host.seq_qlen, self.heads, 1))
         plan = build_plan(host.seq_qlen, host.seq_pos0, self.heads, 1, rows, 0, chunk=0)
@@ -151,6 +174,10 @@ class LatentAttention(Mixer):
                         self.magnitude, self.n_kv, self.eps, H, self.dim, self.rot, self.rank,
                         cache.k_pages, cache.block_table, ctx)
         lk.heads_product(q, self.dim + self.rot, self.w_uk_t, folded, self.row)
+        if ctx.notes[self.key] == -1:
+            sums = ctx.buffer("latent_attention.sums", (n, H * self.row))
+            self.launcher.run(folded, sums, cache.k_pages, cache.k_pages, cache.block_table, ctx)
+            return self._finish(sums, self.row, proj, ctx)
         mixed = ctx.buffer("latent_attention.mixed", (n, H * self.rank), torch.float32)
         if ctx.notes[self.key] == 0:
             rk.chunk_attention_decode(folded, mixed, cache.k_pages, cache.k_pages,
@@ -161,8 +188,15 @@ class LatentAttention(Mixer):
                                ctx.arrays[self.key + "/items"], None, None, H, 1, self.row,
                                self.rank, self.scale, 0, ctx, tile_rows=ctx.notes[self.key],
                                v_stride=self.row)
+        return self._finish(mixed, self.rank, proj, ctx)
+
+    def _finish(self, sums: torch.Tensor, stride: int, proj: torch.Tensor,
+                ctx: StepContext) -> torch.Tensor:
+        """The heads' weighted sums over the latent (head h's at columns h * stride) through
+        W_uv[h], the gate and W_o."""
+        n, H = sums.shape[0], self.heads
         context = ctx.buffer("latent_attention.context", (n, H * self.dv))
-        lk.heads_product(mixed, self.rank, self.w_uv, context, self.dv,
+        lk.heads_product(sums, stride, self.w_uv, context, self.dv,
                          gate=proj[:, self.g_col: self.g_col + H * self.dv])
         out = ctx.buffer("latent_attention.out", (n, self.width))
         ops.linear(context, self.w_o, out=out, status=ctx.status)
