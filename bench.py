@@ -815,13 +815,14 @@ def workload_sebilorn(args, warmup: int, steps: int) -> int:
 
 def vapelix_shape(layers: int) -> dict:
     """A Vapelix model of the headline's width and vocabulary: latent attention (16 heads of 128
-    plain and 64 rotated query/key features, a latent of 256) in every layer, beside a gated dense
+    plain and 64 rotated query/key features, a latent of 192, so that a cached row of 256
+    features fits the tensor-core attention kernels) in every layer, beside a gated dense
     feed-forward of the headline's size in every fourth layer and 16 routed experts, 4 a token,
     in the others (as many active feed-forward weights as the dense layers have); the token's
     side input after every layer.  No loop, so that the layer runs equal the other models'."""
     rot = {"dims": 64, "base": 10000.0,
            "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
-    mixer = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 256,
+    mixer = {"heads": 16, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": 768, "kv_rank": 192,
              "scale": 192 ** -0.5, "rot": rot}
     dense = {"kind": "dense", "ff": MODEL["intermediate_size"]}
     routed = {"kind": "moe", "expert": {"ff": 2048}, "router": {"experts": 16, "top": 4}}
@@ -940,11 +941,31 @@ def vapelix_kernels(peak: dict) -> list[dict]:
                bytes_=n * H * (dim + rank) * 2 + H * rank * dim * 2, flops=2 * n * H * dim * rank,
                like="linear")
         mixed = torch.empty(n, H * rank, device=dev)
+        sums, a_head = mixed, rank
         if n == s and rk.chunk_decode_ok(bf16, H, 1, row, rank, True):
             us = timed(lambda: rk.chunk_attention_decode(folded, mixed, pages, pages, table, None,
                                                          None, H, 1, row, rank, m["scale"], 0, ctx,
                                                          v_stride=row))
+            record("attention over the latent (single tokens)", case, us,
+                   bytes_=read * row * 2 + n * H * (row * 2 + rank * 4),
+                   flops=2 * keys * H * (row + rank), like="attention, 4 key/value heads of 128")
         else:
+            # prompt portions: the tensor-core kernels, one key/value head of `row` features
+            from distengine_b200.kernels.attention import AttentionLauncher
+            from distengine_b200.parts.context import StepPrep, Workspace
+            launcher = AttentionLauncher(bf16, H, 1, row, m["scale"], None)
+            prep = StepPrep(SimpleNamespace(seq_qlen=ctx.host.seq_qlen, seq_pos0=ctx.host.seq_pos0))
+            launcher.prepare(prep, allow_decode=False)
+            workspace = Workspace(torch.device(dev))
+            ctx.notes = prep.notes
+            ctx.arrays = {k: torch.from_numpy(np.ascontiguousarray(v, dtype=np.int32)).to(dev)
+                          for k, v in prep.extra.items()}
+            ctx.buffer = lambda name, shape, dt=None: workspace.get(name, shape, dt or bf16)
+            sums, a_head = torch.empty(n, H * row, dtype=bf16, device=dev), row
+            us = timed(lambda: launcher.run(folded, sums, pages, pages, table, ctx))
+            record("attention over the latent (tensor cores)", case, us,
+                   bytes_=read * row * 2 + n * H * row * 4, tensor_flops=2 * keys * H * 2 * row,
+                   like="attention, 4 key/value heads of 128")
             rows = rk.chunk_rows_per_tile(bf16, row, rank, n > s,
                                           rk.long_portion_rows(ctx.host.seq_qlen, H, 1))
             plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H, 1, rows, 0, chunk=0)
@@ -952,8 +973,9 @@ def vapelix_kernels(peak: dict) -> list[dict]:
             us = timed(lambda: rk.chunk_attention(folded, mixed, pages, pages, table, items, None,
                                                   None, H, 1, row, rank, m["scale"], 0, ctx,
                                                   tile_rows=rows, v_stride=row))
-        record("attention over the latent", case, us, bytes_=read * row * 2 + n * H * (row * 2 + rank * 4),
-               flops=2 * keys * H * (row + rank), like="attention, 4 key/value heads of 128")
+            record("attention over the latent (CUDA cores: float32, other row sizes)", case, us,
+                   bytes_=read * row * 2 + n * H * (row * 2 + rank * 4),
+                   flops=2 * keys * H * (row + rank), like="attention, 4 key/value heads of 128")
         # the like kernel: 16 heads on 4 key/value heads of 128, every earlier token seen
         G, dk = 4, 128
         kp = torch.randn(s * pages_seq, G, page, dk, device=dev).to(bf16)
@@ -963,18 +985,23 @@ def vapelix_kernels(peak: dict) -> list[dict]:
         if n == s and rk.chunk_decode_ok(bf16, H, G, dk, dk):
             us = timed(lambda: rk.chunk_attention_decode(aq, raw, kp, vp, table, None, None, H, G,
                                                          dk, dk, 0.09, 0, ctx))
+            record("attention, 4 key/value heads of 128 (other models)", case, us,
+                   bytes_=read * G * 2 * dk * 2 + n * H * dk * 6, flops=2 * keys * H * 2 * dk)
         else:
-            rows = rk.chunk_rows_per_tile(bf16, dk, dk, n > s,
-                                          rk.long_portion_rows(ctx.host.seq_qlen, H, G))
-            plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, rows, 0, chunk=0)
-            items = torch.from_numpy(plan.items).to(dev)
-            us = timed(lambda: rk.chunk_attention(aq, raw, kp, vp, table, items, None, None, H, G,
-                                                  dk, dk, 0.09, 0, ctx, tile_rows=rows))
-        record("attention, 4 key/value heads of 128 (other models)", case, us,
-               bytes_=read * G * 2 * dk * 2 + n * H * dk * 6, flops=2 * keys * H * 2 * dk)
+            like = AttentionLauncher(bf16, H, G, dk, 0.09, None)
+            prep = StepPrep(SimpleNamespace(seq_qlen=ctx.host.seq_qlen, seq_pos0=ctx.host.seq_pos0))
+            like.prepare(prep, allow_decode=False)
+            ctx.notes = prep.notes
+            ctx.arrays = {k: torch.from_numpy(np.ascontiguousarray(v, dtype=np.int32)).to(dev)
+                          for k, v in prep.extra.items()}
+            ao = torch.empty(n, H * dk, dtype=bf16, device=dev)
+            us = timed(lambda: like.run(aq, ao, kp, vp, table, ctx))
+            record("attention, 4 key/value heads of 128 (other models, tensor cores)", case, us,
+                   bytes_=read * G * 2 * dk * 2 + n * H * dk * 4,
+                   tensor_flops=2 * keys * H * 2 * dk)
         gate = torch.randn(n, H * dv, device=dev).to(bf16)
         context = torch.empty(n, H * dv, dtype=bf16, device=dev)
-        us = timed(lambda: lk.heads_product(mixed, rank, w_uv, context, dv, gate=gate))
+        us = timed(lambda: lk.heads_product(sums, a_head, w_uv, context, dv, gate=gate))
         record("heads_product (values, gated)", case, us,
                bytes_=n * H * (rank * 4 + dv * 4) + H * rank * dv * 2, flops=2 * n * H * dv * rank,
                like="linear")

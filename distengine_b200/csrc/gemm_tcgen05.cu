@@ -167,7 +167,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
         if (lane == 0) {
             int it = 0;
             for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-                const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+                // grouped: the column tiles of a row tile run side by side (they share its rows, and the
+                // row tiles of an expert, which follow one another, its weights)
+                const int tile_m = GROUPED ? tile / tiles_n : tile % tiles_m;
+                const int tile_n = GROUPED ? tile % tiles_n : tile / tiles_m;
                 int w_row0 = tile_n * bn;
                 if (GROUPED) {
                     const int e = tile_expert[tile_m];
@@ -199,7 +202,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
             const unsigned idesc = instr_desc(BM, bn);
             int it = 0, local = -1;
             for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-                if (GROUPED && tile_expert[tile % tiles_m] < 0) continue;
+                if (GROUPED && tile_expert[tile / tiles_n] < 0) continue;
                 ++local;
                 const int buf = local & 1;
                 // the epilogue has read this accumulator's tile before last
@@ -230,7 +233,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x,
         int local = -1;
         if (GROUPED) pdl_wait();                           // tile_expert, pair_of: kernels' outputs
         for (int tile = blockIdx.x; tile < total && ok; tile += gridDim.x) {
-            const int tile_m = tile % tiles_m, tile_n = tile / tiles_m;
+            const int tile_m = GROUPED ? tile / tiles_n : tile % tiles_m;
+            const int tile_n = GROUPED ? tile % tiles_n : tile / tiles_m;
             if (GROUPED && tile_expert[tile_m] < 0) continue;
             ++local;
             const int buf = local & 1;
