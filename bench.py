@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload headline|mixed|long|fp32|vomotar|sebilorn] [--layers L]
+                    [--workload headline|mixed|long|fp32|vomotar|sebilorn|vapelix] [--layers L]
 
 The default (``headline``) has the TinyLlama-1.1B layer sizes in bfloat16.  A step is one decode
 step of a batch of 8 requests whose prompts of 512 tokens are in the cache; K steps are timed with
@@ -40,6 +40,11 @@ Other workloads, each with its own line (the number of layers is named beside th
   vocabulary, beside Vomotar and Llama with the same number of layers: decode at batch 8 and 64
   and a prompt of 2,048 tokens, and every kernel of the design alone against its roofline, each
   beside the like kernel of the other models.
+* ``vapelix``: the Vapelix architecture (latent attention over a cached latent, routed experts
+  beside dense gated feed-forwards, a side input from the token's row of a table; two branches of
+  one input a layer) at the same width and vocabulary, beside Llama with the same number of
+  layers: decode at batch 8 and 64 and a prompt of 2,048 tokens, and every kernel of the design
+  alone against its roofline, each beside the like kernel of the other models.
 """
 
 from __future__ import annotations
