@@ -103,7 +103,7 @@ def _replay(runner, steps, vocab):
         return th.collect(steps, out, vocab)
 
 
-@pytest.mark.parametrize("name", ["vap_a", "vap_b", "vap_c"])
+@pytest.mark.parametrize("name", ["vap_a", "vap_b", "vap_c", "vap_d"])
 @pytest.mark.parametrize("dtype_name", ["float32", "bfloat16"])
 @pytest.mark.parametrize("schedule", ["whole", "tail", "portions", "pairs", "mixed", "mixed_tight"])
 def test_replay_matches_plain(name, dtype_name, schedule, model_root):

@@ -92,6 +92,12 @@ SIZES = [
     ((12, 8, 16, 8, 16, 16, 0.2, 1000000.0, (16.0, 48, 32.0, 1.0)), 16),  # more than 8 heads
     ((1, 32, 4, 1, 8, 60, 0.15, 500.0, (2.0, 32, 4.0, 2.0)), 8),      # one head, values of size 1
     ((5, 4, 32, 24, 40, 8, 0.3, 20.0, None), 32),                     # mostly rotated
+    # cached rows of 64 and of 128 features: in bfloat16 the prompt portions take the tcgen05
+    # attention kernel
+    ((6, 24, 16, 20, 32, 48, 0.2, 10000.0, (8.0, 64, 32.0, 1.0)), 16),
+    ((4, 32, 32, 16, 24, 96, 0.15, 1000000.0, (4.0, 128, 16.0, 2.0)), 16),
+    ((10, 16, 16, 24, 40, 48, 0.2, 10000.0, None), 8),
+    ((3, 40, 48, 8, 16, 208, 0.1, 500.0, None), 16),                  # a row of 256 features
 ]
 
 
@@ -107,8 +113,13 @@ def test_latent_attention_in_portions(dtype, sizes, page):
     assert {k: v[0] for k, v in mixer.tensors().items()} == {k: tuple(v.shape) for k, v in w.items()}
     mixer.load(w)
     spec = mixer.cache_spec()
-    assert (spec.kv_heads, spec.head_dim, spec.v_dim) == (1, m["kv_rank"] + m["rot_dim"],
-                                                          m["kv_rank"])
+    row = m["kv_rank"] + m["rot_dim"]
+    assert (spec.kv_heads, spec.head_dim, spec.v_dim) == (1, row, m["kv_rank"])
+    # which kernels the prompt portions take
+    tensor = dtype == torch.bfloat16 and row % 16 == 0 and row <= 256
+    assert (mixer.launcher is not None) == tensor
+    if tensor:
+        assert (mixer.launcher.shapes[0].code == 2) == (row in (64, 128))
     g = _gen(5)
     xs = {"a": torch.randn(82, width, generator=g).to(dtype),
           "b": torch.randn(46, width, generator=g).to(dtype)}

@@ -85,9 +85,22 @@ VAP_WIDE = {
     ],
 }
 
-ALL = {"vap_a": VAP_A, "vap_b": VAP_B, "vap_c": VAP_C, "vap_wide": VAP_WIDE}
-SEEDS = {"vap_a": 21, "vap_b": 22, "vap_c": 23, "vap_wide": 24}
-PAGES = {"vap_a": 16, "vap_b": 8, "vap_c": 4, "vap_wide": 16}
+# cached rows of 64 and of 128 features (in bfloat16 their prompt portions take the tcgen05
+# attention kernel), layers that differ in every size, a loop over the last two layers
+VAP_D = {
+    "architecture": "Vapelix", "vocab": 200, "width": 96, "norm": {"eps": 1e-6},
+    "token_side": {"dim": 12},
+    "loop": {"start": 1, "stop": 3, "times": 2},
+    "layers": [
+        _layer(_mixer(6, 24, 16, 20, 32, 48, 0.2, 10000.0, (8.0, 64, 32.0, 1.0)), _moe(6, 2, 40)),
+        _layer(_mixer(4, 32, 32, 16, 24, 96, 0.15, 1000000.0, (4.0, 128, 16.0, 2.0)), _dense(128)),
+        _layer(_mixer(10, 16, 16, 24, 40, 48, 0.2, 500.0), _moe(8, 3, 32)),
+    ],
+}
+
+ALL = {"vap_a": VAP_A, "vap_b": VAP_B, "vap_c": VAP_C, "vap_wide": VAP_WIDE, "vap_d": VAP_D}
+SEEDS = {"vap_a": 21, "vap_b": 22, "vap_c": 23, "vap_wide": 24, "vap_d": 25}
+PAGES = {"vap_a": 16, "vap_b": 8, "vap_c": 4, "vap_wide": 16, "vap_d": 16}
 
 
 def write_folder(config: dict, folder: str, weights: dict) -> str:
