@@ -49,7 +49,9 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
 
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* k_s = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [2][KT][LDS]
-    __nv_bfloat16* v_s = k_s + 2 * KT * LDS;                                  // [2][KT][LDS]
+    // values that live in the key pages (a latent that is both) are read from the key tiles
+    const bool same = v_pages == k_pages;
+    __nv_bfloat16* v_s = same ? k_s : k_s + 2 * KT * LDS;                     // [2][KT][LDS]
 
     // blocks are numbered item-major, so that the items run in the order the host gave them
     const WorkItem it = items[blockIdx.x / kv_heads];
@@ -136,7 +138,7 @@ attn_mma_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, __nv_bfloat16
                 else if (status != nullptr) atomicExch(status, 2);   // a visible key has no page
             }
             cp_async16(kd + j * LDS + ch * 8, k_pages + off, ok);
-            cp_async16(vd + j * LDS + ch * 8, v_pages + off, ok);
+            if (!same) cp_async16(vd + j * LDS + ch * 8, v_pages + off, ok);
         }
     };
 
@@ -357,7 +359,8 @@ int launch(const void* q, int q_stride, void* out, int out_stride, const void* k
            const int* seq_slot, const int* seq_qstart, const int* seq_qlen, const int* seq_pos0,
            const int* items, int num_items, float* partial_acc, float* partial_ml, int heads,
            int kv_heads, int page, float scale, int window, int* status, cudaStream_t s) {
-    size_t smem = (size_t)4 * KT * LDS * sizeof(__nv_bfloat16);
+    // two stages of key tiles and, unless the values are in the key pages, of value tiles
+    size_t smem = (size_t)(k_pages == v_pages ? 2 : 4) * KT * LDS * sizeof(__nv_bfloat16);
     const size_t red = (size_t)WN * 16 * (D + 2) * sizeof(float);
     if (WN > 1 && red > smem) smem = red;
     auto kernel = attn_mma_kernel<WM, WN, RT>;
