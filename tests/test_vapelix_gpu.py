@@ -284,6 +284,11 @@ def test_models_of_random_sizes_under_a_mixed_schedule(seed, model_root):
         rows = _replay(runner, steps, config["vocab"])
         runner.cache.check_invariants()
         _compare(rows, want, torch.float32, f"random model {seed} graphs={graphs}")
+    # bfloat16: whichever kernels these sizes take (tensor cores where rows are whole 16-byte
+    # pieces, CUDA cores elsewhere)
+    runner = build_runner(folder, "bfloat16", 256, page_size=16, poison_freed_pages=True)
+    rows, want16 = _replay_and_reference(runner, steps, config, weights, requests, "bfloat16")
+    _compare(rows, want16, torch.bfloat16, f"random model {seed} bfloat16")
 
 
 def _plain_greedy(name, weights, prompt, new):
