@@ -57,6 +57,8 @@ class LayerSpec:
     # what is added to the stream after the layer's branches from the token itself (a kind of the
     # side-input registry), or None; its tensors live under the prefix of role "side_input"
     side_input: "PartSpec | None" = None
+    # the arrangement's own constructor arguments (name, value), for arrangements that have some
+    block_params: tuple[tuple[str, Any], ...] = ()
 
     def prefix(self, role: str) -> str:
         return dict(self.prefixes)[role]
@@ -98,6 +100,11 @@ class ModelConfig:
     def embedding_scale(self) -> float:
         """The embedding rows are multiplied by this as they enter the residual stream."""
         return 1.0
+
+    def embedding_norm(self) -> "PartSpec | None":
+        """A norm on the embedding rows before the first layer (its tensor under the prefix
+        ``tensor_names()["embedding_norm"]``), or None."""
+        return None
 
     @property
     def logit_softcap(self) -> "float | None":

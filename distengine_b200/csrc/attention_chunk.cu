@@ -47,7 +47,15 @@ struct Sight {
     float softcap;      // > 0: score <- softcap * tanh(score / softcap)
     int v_stride;       // elements from one key's values to the next in v_pages: dv, or the key
                         // size where the values are the first dv features of the key rows
+    int linear;         // the distance penalty is r1[h] * (i - j) instead of the logarithmic one
+    const float* sink;  // [heads] or null: the softmax's denominator also holds exp(sink[h]), a
+                        // weight without a key or a value (not scaled, no penalty)
 };
+// 1 / (the row's sum of weights, with the sink's share): m is the row's reference maximum
+__device__ __forceinline__ float sight_inverse(const Sight& s, int head, float m, float l) {
+    if (s.sink != nullptr) l += expf(s.sink[head] - m);
+    return l > 0.0f ? 1.0f / l : 0.0f;
+}
 
 // first key of the near range of a row at `pos` (does not fall as pos grows)
 __device__ __forceinline__ int sight_lo(const Sight& m, int pos) {
@@ -63,7 +71,7 @@ __device__ __forceinline__ int sight_first(const Sight& m, int lo) {
 __device__ __forceinline__ float sight_score(const Sight& m, float s, float scale, float pen1,
                                              float pen2, bool penalty, float dist) {
     s *= scale;
-    if (penalty) s -= pen1 * log1pf(pen2 * dist);
+    if (penalty) s -= m.linear ? pen1 * dist : pen1 * log1pf(pen2 * dist);
     if (m.softcap > 0.0f) s = m.softcap * tanhf(s / m.softcap);
     return s;
 }
@@ -197,13 +205,169 @@ __global__ void kv_write_rotated_kernel(T* __restrict__ proj, int ld, const int*
     pdl_trigger();
 }
 
+// What lies between a mixer's stacked projection and its attention, for mixers that do more to
+// q, k and v than turn them: proj row = [q (H dk) | k (G dk) | v (G dv) | ...], C = (H + G) dk +
+// G dv channels.  In this order, each step optional:
+//   bias      u = proj + bias[c]
+//   taps      a short causal convolution over time on every channel, y_t = sum_j taps[c][j] *
+//             u_(t - K + 1 + j), zeros before the sequence's start; inputs before the step's first
+//             token of the sequence come from the slot's state, kept[i] = projection (without
+//             bias) at position pos0 - (K - 1) + i, as conv_state leaves them
+//   norm      q and k divided by their root mean square (eps inside the root) and weighted: 1 over
+//             every head with weights [dk] that all heads share, 2 over the whole projection with
+//             weights [H dk] and [G dk]
+//   freq      the first `rot` features of every head of q and k turned by position, angle = pos *
+//             freq[i] (formed in double precision), cosine and sine times `magnitude`; pairs are
+//             (2i, 2i + 1) with `adjacent`, else (i, i + rot / 2)
+//   temp      q times 1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)
+//   mix       1: the values (as they are cached) are also left in v_first [N, G dv];
+//             2: v <- (1 - lambda) v + lambda v_first, lambda one number on the device
+// q goes to q_out [N, H dk] in the activation type, k and v into the pages.  All arithmetic is
+// float32.  One block a token; shared memory: C + rot + H + G floats.
+struct Prepare {
+    const float* bias;
+    const float* taps;
+    int K;
+    const float* state;
+    long long slot_stride;
+    int conv_offset;
+    int norm;
+    const float* q_weight;
+    const float* k_weight;
+    float eps;
+    const float* freq;
+    int rot;
+    float magnitude;
+    int adjacent;
+    float temp_coef;
+    int temp_every;
+    int mix;
+    const float* lambda;
+    float* v_first;
+};
+
+template <typename T>
+__global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __restrict__ q_out,
+                                   const int* __restrict__ positions,
+                                   const int* __restrict__ token_seq,
+                                   const int* __restrict__ token_slot,
+                                   const int* __restrict__ seq_pos0, Prepare pp, int H, int G,
+                                   int dk, int dv, T* __restrict__ k_pages, T* __restrict__ v_pages,
+                                   const int* __restrict__ block_table, int table_stride, int page,
+                                   int num_pages, int* __restrict__ status) {
+    extern __shared__ float sh[];
+    __shared__ float scratch[33];
+    const int n = blockIdx.x;
+    const int qk = (H + G) * dk, C = qk + G * dv, half = pp.rot / 2;
+    float* cs_tab = sh + C;                          // [half] cosines, then [half] sines
+    float* inv_s = cs_tab + pp.rot;                  // [H + G]
+    const int pos = positions[n], slot = token_slot[n];
+    const int off = pos - seq_pos0[token_seq[n]];    // the token's place in its sequence's portion
+    const int page_id = block_table[(size_t)slot * table_stride + pos / page];
+    const bool can_write = page_id >= 0 && page_id < num_pages;
+    if (!can_write && threadIdx.x == 0) atomicExch(status, 1);   // never written outside the pool
+    for (int i = threadIdx.x; i < half; i += blockDim.x) {
+        double sn, cs;
+        sincos((double)pos * (double)pp.freq[i], &sn, &cs);
+        cs_tab[i] = (float)cs * pp.magnitude;
+        cs_tab[half + i] = (float)sn * pp.magnitude;
+    }
+    pdl_wait();
+    const T* row = proj + (size_t)n * ld;
+    if (pp.taps != nullptr && pp.K > 1) {
+        const int K = pp.K;
+        const float* kept = pp.state + (size_t)slot * pp.slot_stride + pp.conv_offset;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            const float b = pp.bias ? pp.bias[c] : 0.0f;
+            float acc = 0.0f;
+            for (int j = 0; j < K; ++j) {
+                const int rel = off - (K - 1) + j;
+                if (pos - (K - 1) + j < 0) continue;             // before the sequence's start
+                const float x = rel >= 0 ? to_float(proj[(size_t)(n - (K - 1) + j) * ld + c])
+                                         : kept[(size_t)(off + j) * C + c];
+                acc = fmaf(pp.taps[c * K + j], x + b, acc);
+            }
+            sh[c] = acc;
+        }
+    } else {
+        const float tap = pp.taps != nullptr ? 1.0f : 0.0f;     // a convolution of one tap
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            const float x = to_float(row[c]) + (pp.bias ? pp.bias[c] : 0.0f);
+            sh[c] = tap != 0.0f ? pp.taps[c] * x : x;
+        }
+    }
+    __syncthreads();
+    if (pp.norm == 1) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+        for (int h = warp; h < H + G; h += warps) {
+            float ss = 0.0f;
+            for (int i = lane; i < dk; i += 32) ss = fmaf(sh[h * dk + i], sh[h * dk + i], ss);
+            ss = warp_sum(ss);
+            if (lane == 0) inv_s[h] = 1.0f / sqrtf(ss / (float)dk + pp.eps);
+        }
+    } else if (pp.norm == 2) {
+        float sq = 0.0f, sk = 0.0f;
+        for (int i = threadIdx.x; i < H * dk; i += blockDim.x) sq = fmaf(sh[i], sh[i], sq);
+        for (int i = H * dk + threadIdx.x; i < qk; i += blockDim.x) sk = fmaf(sh[i], sh[i], sk);
+        const float iq = 1.0f / sqrtf(block_sum(sq, scratch) / (float)(H * dk) + pp.eps);
+        const float ik = 1.0f / sqrtf(block_sum(sk, scratch) / (float)(G * dk) + pp.eps);
+        for (int h = threadIdx.x; h < H + G; h += blockDim.x) inv_s[h] = h < H ? iq : ik;
+    }
+    __syncthreads();
+    pdl_trigger();
+    float temp = 1.0f;
+    if (pp.temp_every > 0) temp = 1.0f + pp.temp_coef * logf((float)((pos + 1) / pp.temp_every) + 1.0f);
+    const size_t at = ((size_t)(can_write ? page_id : 0) * G) * page + (size_t)(pos % page);
+    const int per = dk - half;                       // work items a head: pairs, then plain features
+    for (int idx = threadIdx.x; idx < (H + G) * per; idx += blockDim.x) {
+        const int h = idx / per, i = idx - h * per;
+        const bool is_q = h < H;
+        if (!is_q && !can_write) continue;
+        const float* x = sh + h * dk;
+        const float* wt = nullptr;
+        float inv = 1.0f;
+        if (pp.norm != 0) {
+            inv = inv_s[h];
+            wt = is_q ? pp.q_weight : pp.k_weight;
+            if (pp.norm == 2) wt += (is_q ? h : h - H) * dk;
+        }
+        const float mul = is_q ? temp : 1.0f;
+        T* dst = is_q ? q_out + (size_t)n * (H * dk) + h * dk
+                      : k_pages + (at + (size_t)(h - H) * page) * dk;
+        if (i < half) {
+            const int a = pp.adjacent ? 2 * i : i, b = pp.adjacent ? 2 * i + 1 : i + half;
+            float ra, rb;
+            rope_rotate(x[a] * inv * (wt ? wt[a] : 1.0f), x[b] * inv * (wt ? wt[b] : 1.0f),
+                        cs_tab[i], cs_tab[half + i], ra, rb);
+            dst[a] = from_float<T>(ra * mul);
+            dst[b] = from_float<T>(rb * mul);
+        } else {
+            const int a = i + half;
+            dst[a] = from_float<T>(x[a] * inv * (wt ? wt[a] : 1.0f) * mul);
+        }
+    }
+    const float lam = pp.mix == 2 ? pp.lambda[0] : 0.0f;
+    for (int idx = threadIdx.x; idx < G * dv; idx += blockDim.x) {
+        float v = sh[qk + idx];
+        if (pp.mix == 2) v = (1.0f - lam) * v + lam * pp.v_first[(size_t)n * (G * dv) + idx];
+        const T stored = from_float<T>(v);
+        if (pp.mix == 1) pp.v_first[(size_t)n * (G * dv) + idx] = to_float(stored);
+        if (can_write) {
+            const int h = idx / dv, i = idx - h * dv;
+            v_pages[(at + (size_t)h * page) * dv + i] = stored;
+        }
+    }
+}
+
 // After the attention: every head's result (float32 [N, H dv]) turned back by its token's position
 // (pairs (i, i + dv/2), angle -pos * fv[i]; fv null: as it is), times sigmoid(gate) where a gate
-// (type T, row stride ld_gate) is given, rounded to the activation type.  One block a token.
+// (type T, row stride ld_gate; one number a feature, or one a head with gate_per_head) is given,
+// rounded to the activation type.  One block a token.
 template <typename T>
 __global__ void attn_finish_kernel(const float* __restrict__ o, const int* __restrict__ positions,
                                    const float* __restrict__ fv, const T* __restrict__ gate,
-                                   int ld_gate, T* __restrict__ out, int H, int dv) {
+                                   int ld_gate, T* __restrict__ out, int H, int dv,
+                                   int gate_per_head) {
     const int n = blockIdx.x;
     const float fpos = (float)positions[n];
     const float* src = o + (size_t)n * H * dv;
@@ -221,21 +385,21 @@ __global__ void attn_finish_kernel(const float* __restrict__ o, const int* __res
                 sincosf(fpos * fv[i], &sn, &cs);
                 rope_rotate(src[a], src[b], cs, -sn, ra, rb);
                 if (gt) {
-                    ra *= 1.0f / (1.0f + expf(-to_float(gt[a])));
-                    rb *= 1.0f / (1.0f + expf(-to_float(gt[b])));
+                    ra *= 1.0f / (1.0f + expf(-to_float(gt[gate_per_head ? h : a])));
+                    rb *= 1.0f / (1.0f + expf(-to_float(gt[gate_per_head ? h : b])));
                 }
                 dst[a] = from_float<T>(ra);
                 dst[b] = from_float<T>(rb);
             } else {
                 float x = src[b];
-                if (gt) x *= 1.0f / (1.0f + expf(-to_float(gt[b])));
+                if (gt) x *= 1.0f / (1.0f + expf(-to_float(gt[gate_per_head ? h : b])));
                 dst[b] = from_float<T>(x);
             }
         }
     } else {
         for (int idx = threadIdx.x; idx < H * dv; idx += blockDim.x) {
             float x = src[idx];
-            if (gt) x *= 1.0f / (1.0f + expf(-to_float(gt[idx])));
+            if (gt) x *= 1.0f / (1.0f + expf(-to_float(gt[gate_per_head ? idx / dv : idx])));
             dst[idx] = from_float<T>(x);
         }
     }
@@ -350,7 +514,7 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out,
     }
     pdl_trigger();
     if (!active) return;
-    const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+    const float inv = sight_inverse(sight, hq, m, l);
     const size_t o = (size_t)(tok0 + t) * out_stride + hq * dv;
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
@@ -582,7 +746,7 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ 
 #pragma unroll
     for (int i = 0; i < RW; ++i) {
         if (!active[i]) continue;
-        const float inv = l[i] > 0.0f ? 1.0f / l[i] : 0.0f;
+        const float inv = sight_inverse(sight, hq[i], m[i], l[i]);
         const size_t o = (size_t)(tok0 + tok[i]) * out_stride + hq[i] * dv;
 #pragma unroll
         for (int b = 0; b < MAX_D / 128; ++b) {
@@ -842,7 +1006,7 @@ attn_chunk_tiled_kernel(const T* __restrict__ q, int q_stride, void* __restrict_
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
         if (!active[e]) continue;
-        const float inv = l[e] > 0.0f ? 1.0f / l[e] : 0.0f;
+        const float inv = sight_inverse(sight, hq[e], m[e], l[e]);
         const size_t o = (size_t)(tok0 + tok[e]) * out_stride + hq[e] * dv;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
@@ -1127,7 +1291,7 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
                 if (dd < dv) res[b] = fmaf(Pacc[(size_t)(w * RW + i) * dv + dd], f, res[b]);
             }
         }
-        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+        const float inv = sight_inverse(sight, h0 + i, top, sum);
         const size_t o = (size_t)tok * out_stride + (h0 + i) * dv;
         if (fuse.on) {
             // the head's result through shared memory (the place of the first warp's share of
@@ -1234,12 +1398,13 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
                                    int page, float scale, int chunk, int window, int keep_first,
                                    float softcap, int out_f32, int fused, const float* fk, int rot,
                                    const float* fv, int write_kv, const void* gate, int ld_gate,
-                                   int v_stride, int* status, void* stream) {
+                                   int v_stride, int linear, const float* sink, int* status,
+                                   void* stream) {
     if (n_seqs <= 0) return 0;
     // v_stride 0: values in rows of their own; else rows of v_pages are that many elements apart
     const int pn_v = dtype == DE_BF16 ? 8 : 4;
     if (v_stride != 0 && (v_stride < dv || v_stride % pn_v != 0 || fused)) return -2;
-    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv};
+    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv, linear, sink};
     const Fuse fuse = {fused, fk, rot, fv, write_kv, gate, ld_gate};
     if (fused && (rot < 0 || rot % 2 || rot > dk || (fv != nullptr && dv % 2) || out_f32)) return -2;
     const int v_in_k = v_pages == k_pages && v_stride == dk;
@@ -1317,9 +1482,51 @@ DE_EXPORT int de_kv_write_rotated(int dtype, void* proj, int ld, const int* posi
                      (float*)v_pages, block_table, table_stride, page, num_pages, write_kv, status);
 }
 
+DE_EXPORT int de_qkv_prepare(int dtype, const void* proj, int ld, void* q_out,
+                             const int* positions, const int* token_seq, const int* token_slot,
+                             const int* seq_pos0, const float* bias, const float* taps, int K,
+                             const float* state, long long slot_stride, int conv_offset, int norm,
+                             const float* q_weight, const float* k_weight, float eps,
+                             const float* freq, int rot, float magnitude, int adjacent,
+                             float temp_coef, int temp_every, int mix, const float* lambda,
+                             float* v_first, int H, int G, int dk, int dv, void* k_pages,
+                             void* v_pages, const int* block_table, int table_stride, int page,
+                             int num_pages, int n, int* status, void* stream) {
+    if (n <= 0) return 0;
+    if (rot < 0 || rot % 2 || rot > dk || (rot > 0 && freq == nullptr) || norm < 0 || norm > 2 ||
+        (norm != 0 && (q_weight == nullptr || k_weight == nullptr)) || mix < 0 || mix > 2 ||
+        (mix != 0 && v_first == nullptr) || (mix == 2 && lambda == nullptr) ||
+        (taps != nullptr && (K < 1 || (K > 1 && state == nullptr))))
+        return -2;
+    const Prepare pp = {bias, taps, K, state, slot_stride, conv_offset, norm, q_weight, k_weight,
+                        eps, freq, rot, magnitude, adjacent, temp_coef, temp_every, mix, lambda,
+                        v_first};
+    cudaStream_t s = (cudaStream_t)stream;
+    const int C = (H + G) * dk + G * dv;
+    const size_t smem = (size_t)(C + rot + H + G) * sizeof(float);
+    if (smem > 200 * 1024) return -2;
+    const int threads = n >= 512 ? 128 : (C >= 2048 ? 512 : 256);
+#define PREP(T)                                                                                 \
+    do {                                                                                        \
+        if (smem > 48 * 1024) {                                                                 \
+            cudaError_t e = cudaFuncSetAttribute(qkv_prepare_kernel<T>,                         \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                                                 (int)smem);                                    \
+            if (e != cudaSuccess) return (int)e;                                                \
+        }                                                                                       \
+        return de_launch(qkv_prepare_kernel<T>, dim3(n), dim3(threads), smem, s, (const T*)proj, \
+                         ld, (T*)q_out, positions, token_seq, token_slot, seq_pos0, pp, H, G,   \
+                         dk, dv, (T*)k_pages, (T*)v_pages, block_table, table_stride, page,     \
+                         num_pages, status);                                                    \
+    } while (0)
+    if (dtype == DE_BF16) PREP(__nv_bfloat16);
+    PREP(float);
+#undef PREP
+}
+
 DE_EXPORT int de_attn_finish(int dtype, const float* o, const int* positions, const float* fv,
                              const void* gate, int ld_gate, void* out, int n, int H, int dv,
-                             void* stream) {
+                             int gate_per_head, void* stream) {
     if (n <= 0) return 0;
     if (fv != nullptr && dv % 2) return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -1327,9 +1534,9 @@ DE_EXPORT int de_attn_finish(int dtype, const float* o, const int* positions, co
     if (dtype == DE_BF16)
         return de_launch(attn_finish_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s, o,
                          positions, fv, (const __nv_bfloat16*)gate, ld_gate, (__nv_bfloat16*)out, H,
-                         dv);
+                         dv, gate_per_head);
     return de_launch(attn_finish_kernel<float>, dim3(n), dim3(threads), 0, s, o, positions, fv,
-                     (const float*)gate, ld_gate, (float*)out, H, dv);
+                     (const float*)gate, ld_gate, (float*)out, H, dv, gate_per_head);
 }
 
 DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, int out_stride,
@@ -1339,12 +1546,13 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
                             const int* items, int num_items, const float* r1, const float* r2,
                             int heads, int kv_heads, int dk, int dv, int page, float scale,
                             int chunk, int window, int keep_first, float softcap, int out_f32,
-                            int tile_rows, int v_stride, int* status, void* stream) {
+                            int tile_rows, int v_stride, int linear, const float* sink,
+                            int* status, void* stream) {
     if (num_items <= 0) return 0;
     // v_stride 0: values in rows of their own; else rows of v_pages are that many elements apart
     if (v_stride != 0 && (v_stride < dv || (vec_ok(dtype, dk, dv) && v_stride % (dtype == DE_BF16 ? 8 : 4))))
         return -2;
-    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv};
+    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv, linear, sink};
     if (dk <= 0 || dk > MAX_DK || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     if (tile_rows != ROWS && !((tile_rows == ROWS * 4 && vec_fits(dtype, dk, dv)) ||

@@ -8,6 +8,13 @@
 //   down     y[pair] = W_down[e] inner[slot]
 //   combine  out[n] = sum_k weight[n, k] * y[n * top + k]   float32, in the order of the choices
 //
+// A second way to score (`mode` 1): s = softmax(z) over all router outputs, the choice goes by
+// s + bias (a correction that does not enter the weights), the weights are the chosen s as they
+// are.  The router may have more outputs than there are experts: the outputs from `experts` on
+// stand for experts that hand their input on (the grouping leaves their pairs out, `combine` adds
+// weight * h for them).  An expert's up product may have no activation (kind 5), for experts whose
+// gate and up rows are stacked and joined by a kernel after the product.
+//
 // Every output element is one chain of multiply-adds over its inputs in ascending order, and a
 // token's result does not depend on which tokens share its tile, its expert or its step.  The
 // number of tiles that are launched depends on the number of tokens only (tiles without an expert
@@ -31,7 +38,7 @@ constexpr int ROUTE_WARPS = 8;
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_WARPS * 32)
 route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w,
-             const float* __restrict__ bias, int n, int width, int experts, int top,
+             const float* __restrict__ bias, int n, int width, int experts, int top, int mode,
              int* __restrict__ chosen, float* __restrict__ weight) {
     extern __shared__ float zs[];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -73,12 +80,27 @@ route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w,
         float t = 0.0f;
 #pragma unroll
         for (int k = 0; k < ROUTE_WARPS; ++k) t += zs[(size_t)k * experts + e];
-        z[e] = t + bias[e];
+        z[e] = mode == 1 ? t : t + bias[e];
     }
     __syncthreads();
     if (warp != 0) return;
     float best[MAX_TOP];
     float total = 0.0f;
+    if (mode == 1) {
+        // scores over all outputs; z becomes score + correction, the scores stay in zs
+        float top_z = -INFINITY;
+        for (int e = lane; e < experts; e += 32) top_z = fmaxf(top_z, z[e]);
+        top_z = warp_max(top_z);
+        float sum = 0.0f;
+        for (int e = lane; e < experts; e += 32) sum += expf(z[e] - top_z);
+        sum = warp_sum(sum);
+        for (int e = lane; e < experts; e += 32) {
+            const float sc = expf(z[e] - top_z) / sum;
+            zs[e] = sc;
+            z[e] = sc + bias[e];
+        }
+        __syncwarp();
+    }
     for (int k = 0; k < top; ++k) {
         float v = -INFINITY;
         int at = 0x7fffffff;
@@ -99,6 +121,12 @@ route_kernel(const T* __restrict__ h, int ldh, const float* __restrict__ w,
             z[at] = -INFINITY;
         }
         __syncwarp();
+    }
+    if (mode == 1) {
+        if (lane == 0)
+            for (int k = 0; k < top; ++k)
+                weight[(size_t)row * top + k] = zs[chosen[(size_t)row * top + k]];
+        return;
     }
     for (int k = 0; k < top; ++k) total += expf(best[k] - best[0]);
     if (lane == 0)
@@ -176,7 +204,8 @@ expert_up_kernel(const T* __restrict__ h, int ldh, const T* __restrict__ up,
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int c = c0 + tc * 4 + j;
-            if (c < ff) inner[(size_t)(s0 + r) * ff + c] = from_float<T>(de_activate(acc[i][j], act));
+            if (c < ff) inner[(size_t)(s0 + r) * ff + c] =
+                from_float<T>(act == 5 ? acc[i][j] : de_activate(acc[i][j], act));
         }
     }
 }
@@ -238,9 +267,13 @@ __global__ void gather_kernel(const T* __restrict__ h, int ldh, const int* __res
     }
 }
 
+// chosen / experts / h: a pair whose choice is not below `experts` adds weight * h[n] (an expert
+// that hands its input on); chosen null: every pair has a row of y.
 template <typename T>
 __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict__ weight, int top,
-                               int width, size_t total, float* __restrict__ out) {
+                               int width, size_t total, float* __restrict__ out,
+                               const int* __restrict__ chosen, int experts,
+                               const T* __restrict__ h, int ldh) {
     pdl_wait();
     pdl_trigger();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -248,8 +281,12 @@ __global__ void combine_kernel(const T* __restrict__ y, const float* __restrict_
         const size_t n = idx / width;
         const int i = (int)(idx - n * width);
         float s = 0.0f;
-        for (int k = 0; k < top; ++k)
-            s = fmaf(weight[n * top + k], to_float(y[(n * top + k) * width + i]), s);
+        for (int k = 0; k < top; ++k) {
+            const bool hands_on = chosen != nullptr && chosen[n * top + k] >= experts;
+            const float v = hands_on ? to_float(h[n * ldh + i])
+                                     : to_float(y[(n * top + k) * width + i]);
+            s = fmaf(weight[n * top + k], v, s);
+        }
         out[idx] = s;
     }
 }
@@ -265,7 +302,7 @@ DE_EXPORT int de_experts_tiles(int n, int top, int experts, int seg) {
 
 DE_EXPORT int de_experts_route(int dtype, const void* h, int ldh, const float* w,
                                const float* bias, int n, int width, int experts, int top,
-                               int* chosen, float* weight, void* stream) {
+                               int mode, int* chosen, float* weight, void* stream) {
     if (n <= 0) return 0;
     if (top <= 0 || top > MAX_TOP || top > experts || experts > 1024) return -2;
     cudaStream_t s = (cudaStream_t)stream;
@@ -274,10 +311,10 @@ DE_EXPORT int de_experts_route(int dtype, const void* h, int ldh, const float* w
     const dim3 grid(n);
     if (dtype == DE_BF16)
         return de_launch(route_kernel<__nv_bfloat16>, grid, dim3(warps * 32), smem, s,
-                         (const __nv_bfloat16*)h, ldh, w, bias, n, width, experts, top, chosen,
-                         weight);
+                         (const __nv_bfloat16*)h, ldh, w, bias, n, width, experts, top, mode,
+                         chosen, weight);
     return de_launch(route_kernel<float>, grid, dim3(warps * 32), smem, s, (const float*)h, ldh, w,
-                     bias, n, width, experts, top, chosen, weight);
+                     bias, n, width, experts, top, mode, chosen, weight);
 }
 
 DE_EXPORT int de_experts_group(const int* chosen, int pairs, int experts, int tiles, int seg,
@@ -306,7 +343,7 @@ DE_EXPORT int de_experts_up(int dtype, const void* h, int ldh, const void* up, c
                             const int* tile_expert, int tiles, int top, int width, int ff,
                             void* inner, int act, void* stream) {
     if (tiles <= 0) return 0;
-    if (act < 0 || act > 4) return -2;
+    if (act < 0 || act > 5) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     const int size = dtype == DE_BF16 ? 2 : 4;
     const int vec_a = ((uintptr_t)h % (4 * size) == 0) && ldh % 4 == 0;
@@ -342,7 +379,8 @@ DE_EXPORT int de_experts_down(int dtype, const void* inner, const void* down, co
 }
 
 DE_EXPORT int de_experts_combine(int dtype, const void* y, const float* weight, int n, int top,
-                                 int width, float* out, void* stream) {
+                                 int width, float* out, const int* chosen, int experts,
+                                 const void* h, int ldh, void* stream) {
     if (n <= 0) return 0;
     const size_t total = (size_t)n * width;
     size_t blocks = (total + 255) / 256;
@@ -350,7 +388,9 @@ DE_EXPORT int de_experts_combine(int dtype, const void* y, const float* weight, 
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == DE_BF16)
         return de_launch(combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s,
-                         (const __nv_bfloat16*)y, weight, top, width, total, out);
+                         (const __nv_bfloat16*)y, weight, top, width, total, out, chosen, experts,
+                         (const __nv_bfloat16*)h, ldh);
     return de_launch(combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s,
-                     (const float*)y, weight, top, width, total, out);
+                     (const float*)y, weight, top, width, total, out, chosen, experts,
+                     (const float*)h, ldh);
 }

@@ -42,6 +42,7 @@ MODULES: dict[str, tuple[str, tuple[str, ...]]] = {
     "recurrent": ("recurrent.cu", ()),
     "latent": ("latent.cu", ()),
     "experts": ("experts.cu", ()),
+    "sublayer": ("sublayer.cu", ()),
 }
 
 

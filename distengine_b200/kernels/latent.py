@@ -72,10 +72,14 @@ def experts_tiles(n: int, top: int, experts: int, segment: int = SEGMENT) -> int
 
 
 def experts_route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top: int,
-                  chosen: torch.Tensor, weight: torch.Tensor) -> None:
+                  chosen: torch.Tensor, weight: torch.Tensor,
+                  scoring: str = "chosen_logits") -> None:
     """chosen [N, top] (int32): the experts with the largest logits router h + bias (float32);
-    weight [N, top] (float32): the softmax over those logits alone."""
+    weight [N, top] (float32): the softmax over those logits alone.  ``scoring``
+    "corrected_scores": the scores are the softmax of router h over all outputs, the choice goes
+    by score + bias, and the weights are the chosen scores as they are."""
     n, experts = h.shape[0], router.shape[0]
+    _need(scoring in ("chosen_logits", "corrected_scores"), "experts_route: unknown scoring")
     _i32(chosen, "chosen")
     _need(h.stride(1) == 1 and router.dtype == bias.dtype == weight.dtype == torch.float32
           and router.is_contiguous() and router.shape[1] == h.shape[1] and bias.is_contiguous()
@@ -83,7 +87,8 @@ def experts_route(h: torch.Tensor, router: torch.Tensor, bias: torch.Tensor, top
           and weight.is_contiguous(), "experts_route: h [N, D], router float32 [E, D], bias [E]")
     lib = library.load("experts")
     _check(lib.de_experts_route(_tag(h.dtype), h.data_ptr(), h.stride(0), router.data_ptr(),
-                                bias.data_ptr(), n, h.shape[1], experts, top, chosen.data_ptr(),
+                                bias.data_ptr(), n, h.shape[1], experts, top,
+                                int(scoring == "corrected_scores"), chosen.data_ptr(),
                                 weight.data_ptr(), _stream()), "experts_route")
 
 
@@ -105,17 +110,21 @@ def experts_group(chosen: torch.Tensor, experts: int, pair_of: torch.Tensor,
 
 
 def experts_up(h: torch.Tensor, up: torch.Tensor, pair_of: torch.Tensor,
-               tile_expert: torch.Tensor, top: int, inner: torch.Tensor, act: str) -> None:
-    """inner[slot] = act(up[e] h[token of the slot's pair]); up [E, ff, D], inner [slots, ff]."""
+               tile_expert: torch.Tensor, top: int, inner: torch.Tensor,
+               act: "str | None") -> None:
+    """inner[slot] = act(up[e] h[token of the slot's pair]); up [E, ff, D], inner [slots, ff];
+    ``act`` None: the product as it is."""
     experts, ff, width = up.shape
     tiles = tile_expert.shape[0]
     _need(up.is_contiguous() and h.stride(1) == 1 and h.shape[1] == width and inner.is_contiguous()
           and inner.shape == (tiles * 64, ff) and h.dtype == up.dtype == inner.dtype
-          and act in ACTIVATIONS, "experts_up: h [N, D], up [E, ff, D], inner [slots, ff]")
+          and (act is None or act in ACTIVATIONS),
+          "experts_up: h [N, D], up [E, ff, D], inner [slots, ff]")
     lib = library.load("experts")
     _check(lib.de_experts_up(_tag(h.dtype), h.data_ptr(), h.stride(0), up.data_ptr(),
                              pair_of.data_ptr(), tile_expert.data_ptr(), tiles, top, width, ff,
-                             inner.data_ptr(), ACTIVATIONS[act], _stream()), "experts_up")
+                             inner.data_ptr(), 5 if act is None else ACTIVATIONS[act],
+                             _stream()), "experts_up")
 
 
 def experts_down(inner: torch.Tensor, down: torch.Tensor, pair_of: torch.Tensor,
@@ -177,12 +186,23 @@ def experts_product(rows: torch.Tensor, w: torch.Tensor, pair_of: torch.Tensor,
                                        status.data_ptr(), _stream()), "experts_product")
 
 
-def experts_combine(y: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """out[n] = sum_k weight[n, k] * y[n * top + k] in float32; out float32 [N, D]."""
+def experts_combine(y: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                    hands_on: "tuple | None" = None) -> None:
+    """out[n] = sum_k weight[n, k] * y[n * top + k] in float32; out float32 [N, D].
+    ``hands_on`` = (chosen [N, top], experts, h [N, D]): a pair whose choice is not below
+    ``experts`` has no row in y; it adds weight * h[n]."""
     n, top = weight.shape
+    extra = (None, 0, None, 0)
+    if hands_on is not None:
+        chosen, experts, h = hands_on
+        _i32(chosen, "chosen")
+        _need(chosen.shape == (n, top) and h.dtype == y.dtype and h.stride(1) == 1
+              and h.shape == (n, out.shape[1]), "experts_combine: chosen [N, top], h [N, D]")
+        extra = (chosen.data_ptr(), int(experts), h.data_ptr(), h.stride(0))
     _need(y.is_contiguous() and y.shape == (n * top, out.shape[1]) and out.is_contiguous()
           and out.dtype == weight.dtype == torch.float32 and out.shape[0] == n
           and weight.is_contiguous(), "experts_combine: y [N top, D], weight [N, top], out [N, D]")
     lib = library.load("experts")
     _check(lib.de_experts_combine(_tag(y.dtype), y.data_ptr(), weight.data_ptr(), n, top,
-                                  out.shape[1], out.data_ptr(), _stream()), "experts_combine")
+                                  out.shape[1], out.data_ptr(), *extra, _stream()),
+           "experts_combine")

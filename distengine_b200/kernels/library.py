@@ -76,12 +76,14 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_chunk_rows": [I, I, I, I],
         "de_attn_chunk_decode_ok": [I, I, I, I, I, I],
         "de_attn_chunk_decode": [I, P, I, P, I, P, P, P, I, I, P, P, P, I, P, P, I, I, I, I, I, F,
-                                 I, I, I, F, I, I, P, I, P, I, P, I, I, P, P],
+                                 I, I, I, F, I, I, P, I, P, I, P, I, I, I, P, P, P],
         "de_kv_write_rotated": [I, P, I, P, P, P, I, P, I, I, I, I, P, P, P, I, I, I, I, I, P, P],
-        "de_attn_finish": [I, P, P, P, P, I, P, I, I, I, P],
+        "de_attn_finish": [I, P, P, P, P, I, P, I, I, I, I, P],
+        "de_qkv_prepare": [I, P, I, P, P, P, P, P, P, P, I, P, L, I, I, P, P, F, P, I, F, I, F, I,
+                           I, P, P, I, I, I, I, P, P, P, I, I, I, I, P, P],
         "de_kv_write_normed": [I, P, I, I, P, P, I, I, I, F, P, P, P, I, I, I, I, P, P],
         "de_attn_chunk": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F,
-                          I, I, I, F, I, I, I, P, P],
+                          I, I, I, F, I, I, I, I, P, P, P],
     },
     "recurrent": {
         "de_recurrent_max_key_dim": [],
@@ -104,11 +106,17 @@ SIGNATURES: dict[str, dict[str, list]] = {
     "experts": {
         "de_experts_tiles": [I, I, I, I],
         "de_experts_gather": [I, P, I, P, I, I, I, P, P],
-        "de_experts_route": [I, P, I, P, P, I, I, I, I, P, P, P],
+        "de_experts_route": [I, P, I, P, P, I, I, I, I, I, P, P, P],
         "de_experts_group": [P, I, I, I, I, P, P, P, P],
         "de_experts_up": [I, P, I, P, P, P, I, I, I, I, P, I, P],
         "de_experts_down": [I, P, P, P, P, I, I, I, P, P],
-        "de_experts_combine": [I, P, P, I, I, I, P, P],
+        "de_experts_combine": [I, P, P, I, I, I, P, P, I, P, I, P],
+    },
+    "sublayer": {
+        "de_norm_stream": [I, I, P, P, P, I, I, F, P],
+        "de_gated_normed_add": [I, I, I, P, P, I, P, P, P, P, P, I, I, F, P],
+        "de_depth_mix": [I, P, L, P, I, L, P, P, P],
+        "de_poly_norm": [I, P, I, P, P, I, I, I, F, P],
     },
     "attention_decode": {
         "de_attn_decode_head_dim": [], "de_attn_decode_max_cluster": [],

@@ -246,6 +246,80 @@ def rmsnorm_cols(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.T
 
 
 # ------------------------------------------------------------------------------- rotation + cache write
+def _wtag(weight: torch.Tensor) -> int:
+    _need(weight.dtype in (torch.float32, torch.bfloat16) and weight.is_contiguous(),
+          "a norm's weight is contiguous float32 or bfloat16")
+    return _tag(weight.dtype)
+
+
+def norm_stream(resid: torch.Tensor, weight: torch.Tensor, eps: float,
+                rows: "torch.Tensor | None" = None) -> None:
+    """resid <- resid / sqrt(mean(resid^2) + eps) * weight row by row, in place on the float32
+    stream; ``rows`` [N, width] (bfloat16 or float32) also receives the result, rounded."""
+    n, width = resid.shape
+    _need(resid.dtype == torch.float32 and resid.is_contiguous() and weight.shape == (width,),
+          "norm_stream: resid float32 [N, width], weight [width]")
+    _need(rows is None or (rows.is_contiguous() and rows.shape == resid.shape),
+          "norm_stream: rows [N, width]")
+    lib = library.load("sublayer")
+    _check(lib.de_norm_stream(_tag(rows.dtype) if rows is not None else 0, _wtag(weight),
+                              resid.data_ptr(), weight.data_ptr(), _ptr(rows), n, width,
+                              float(eps), _stream()), "norm_stream")
+
+
+def gated_normed_add(y: torch.Tensor, gate: torch.Tensor, bias: torch.Tensor, weight: torch.Tensor,
+                     eps: float, resid: torch.Tensor, out: torch.Tensor,
+                     rows: "torch.Tensor | None" = None) -> None:
+    """out = resid + g / sqrt(mean(g^2) + eps) * weight with g = y * sigmoid(gate + bias), row by
+    row in float32.  y [N, width] (the gate's dtype or float32), gate [N, width] (row stride
+    free), bias float32 [width]; resid and out float32 [N, width] (the same tensor or two);
+    ``rows`` of gate's dtype also receives out, rounded."""
+    n, width = out.shape
+    _need(resid.dtype == out.dtype == bias.dtype == torch.float32 and resid.is_contiguous()
+          and out.is_contiguous() and resid.shape == out.shape and bias.shape == (width,)
+          and bias.is_contiguous() and weight.shape == (width,),
+          "gated_normed_add: resid, out float32 [N, width], bias and weight [width]")
+    _need(y.is_contiguous() and y.shape == out.shape and gate.shape == out.shape
+          and gate.stride(1) == 1 and y.dtype in (gate.dtype, torch.float32),
+          "gated_normed_add: y and gate [N, width]")
+    _need(rows is None or (rows.is_contiguous() and rows.shape == out.shape
+                           and rows.dtype == gate.dtype), "gated_normed_add: rows [N, width]")
+    lib = library.load("sublayer")
+    _check(lib.de_gated_normed_add(_tag(gate.dtype), _tag(y.dtype), _wtag(weight), y.data_ptr(),
+                                   gate.data_ptr(), gate.stride(0), bias.data_ptr(),
+                                   weight.data_ptr(), resid.data_ptr(), out.data_ptr(), _ptr(rows),
+                                   n, width, float(eps), _stream()), "gated_normed_add")
+
+
+def depth_mix(history: torch.Tensor, coef: torch.Tensor, out: torch.Tensor,
+              rows: "torch.Tensor | None" = None) -> None:
+    """out = sum_j coef[j] * history[j]; history float32 [count, N, width] (contiguous), coef
+    float32 [count], out float32 [N, width]; ``rows`` also receives out, rounded."""
+    count = history.shape[0]
+    _need(history.dtype == out.dtype == coef.dtype == torch.float32 and history.is_contiguous()
+          and out.is_contiguous() and tuple(history.shape[1:]) == tuple(out.shape)
+          and coef.shape == (count,) and coef.is_contiguous(),
+          "depth_mix: history float32 [count, N, width], coef [count], out [N, width]")
+    _need(rows is None or (rows.is_contiguous() and rows.shape == out.shape),
+          "depth_mix: rows [N, width]")
+    lib = library.load("sublayer")
+    _check(lib.de_depth_mix(_tag(rows.dtype) if rows is not None else 0, history.data_ptr(),
+                            out.numel(), coef.data_ptr(), count, out.numel(), out.data_ptr(),
+                            _ptr(rows), _stream()), "depth_mix")
+
+
+def poly_norm(z: torch.Tensor, coef: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out = a N(z) + b N(z^2) + c N(z^3) + e with coef = (a, b, c, e) float32 on the device and N
+    dividing a row by its root mean square (eps inside the root); float32 arithmetic."""
+    _need(z.dim() == 2 and z.stride(1) == 1 and out.stride(1) == 1 and out.shape == z.shape
+          and out.dtype == z.dtype and coef.dtype == torch.float32 and coef.shape == (4,),
+          "poly_norm: z and out [N, cols] of one dtype, coef float32 [4]")
+    lib = library.load("sublayer")
+    _check(lib.de_poly_norm(_tag(z.dtype), z.data_ptr(), z.stride(0), coef.data_ptr(),
+                            out.data_ptr(), out.stride(0), z.shape[0], z.shape[1], float(eps),
+                            _stream()), "poly_norm")
+
+
 def rope_kv_write(qkv: torch.Tensor, positions: torch.Tensor, token_slot: torch.Tensor,
                   inv_freq: "torch.Tensor | None", rotary_dim: int, heads: int, kv_heads: int,
                   head_dim: int, k_pages: torch.Tensor, v_pages: torch.Tensor,

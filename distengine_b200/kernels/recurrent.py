@@ -236,11 +236,22 @@ def mean_of_normed(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
 
 
 # ------------------------------------------------------------------------------- chunk attention
-def _penalty(r1, r2, heads: int) -> None:
+def _penalty(r1, r2, heads: int, slopes=None, sink=None):
+    """The penalty's two pointers and the kernels' last arguments (linear, sink): either
+    r1 log(1 + r2 distance) or ``slopes`` [heads] times the distance; ``sink`` [heads]: the
+    softmax's denominator also holds exp(sink)."""
     _need((r1 is None) == (r2 is None), "attention: r1 and r2 come together")
+    _need(r1 is None or slopes is None, "attention: one distance penalty, not two")
     if r1 is not None:
         _f32(r1, "r1"), _f32(r2, "r2")
         _need(r1.shape == r2.shape == (heads,), "attention: r1, r2 [heads]")
+    for t, name in ((slopes, "slopes"), (sink, "sink")):
+        if t is not None:
+            _f32(t, name)
+            _need(t.shape == (heads,) and t.is_contiguous(), f"attention: {name} [heads]")
+    if slopes is not None:
+        return slopes, slopes, (1, _ptr(sink))
+    return r1, r2, (0, _ptr(sink))
 
 
 def chunk_rows_per_tile(dtype: torch.dtype, key_dim: int, value_dim: int, wide: bool,
@@ -283,7 +294,9 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                            r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                            value_dim: int, scale: float, chunk: int, ctx, window: int = 0,
                            keep_first: int = 0, softcap: float = 0.0,
-                           fused: "dict | None" = None, v_stride: int = 0) -> None:
+                           fused: "dict | None" = None, v_stride: int = 0,
+                           slopes: "torch.Tensor | None" = None,
+                           sink: "torch.Tensor | None" = None) -> None:
     """``chunk_attention`` for a step in which every sequence brings one token: a block a
     (sequence, kv head), its warps share the key tiles out; no work items.
 
@@ -301,7 +314,7 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
           and out.shape[1] == heads * value_dim and q.shape[0] == ctx.n_seqs,
           "chunk_attention_decode: q, out and pages; one token a sequence")
     _i32(block_table, "block_table")
-    _penalty(r1, r2, heads)
+    r1, r2, last = _penalty(r1, r2, heads, slopes, sink)
     extra = (0, None, 0, None, 0, None, 0)
     if fused is not None:
         fk, rot, fv, gate = fused["fk"], fused["rotary_dim"], fused["fv"], fused["gate"]
@@ -332,7 +345,8 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                                     key_dim, value_dim, k_pages.shape[2], float(scale),
                                     int(chunk), int(window), int(keep_first), float(softcap),
                                     int(out.dtype == torch.float32 and q.dtype != torch.float32),
-                                    *extra, int(v_stride), ctx.status.data_ptr(), _stream()),
+                                    *extra, int(v_stride), *last, ctx.status.data_ptr(),
+                                    _stream()),
            "chunk_attention_decode")
 
 
@@ -363,7 +377,8 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                     r1: torch.Tensor, r2: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                     value_dim: int, scale: float, chunk: int, ctx, tile_rows: int = 8,
                     window: int = 0, keep_first: int = 0, softcap: float = 0.0,
-                    v_stride: int = 0) -> None:
+                    v_stride: int = 0, slopes: "torch.Tensor | None" = None,
+                    sink: "torch.Tensor | None" = None) -> None:
     """Attention of the step's rows over the pages: q rows of [heads dk] at the front of ``q``
     (row stride free), out [N, heads dv]; ``tile_rows``: the rows of a tile that ``items`` were
     cut for (``chunk_rows_per_tile``); ``v_stride`` as in ``chunk_attention_decode``; see
@@ -372,7 +387,7 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
           and out.dtype in (q.dtype, torch.float32)
           and out.shape[1] == heads * value_dim, "chunk_attention: q, out and pages")
     _i32(block_table, "block_table"), _i32(items, "items")
-    _penalty(r1, r2, heads)
+    r1, r2, last = _penalty(r1, r2, heads, slopes, sink)
     lib = library.load("attention_chunk")
     _check(lib.de_attn_chunk(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
                              out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),
@@ -383,7 +398,8 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                              key_dim, value_dim, k_pages.shape[2], float(scale), int(chunk),
                              int(window), int(keep_first), float(softcap),
                              int(out.dtype == torch.float32 and q.dtype != torch.float32),
-                             int(tile_rows), int(v_stride), ctx.status.data_ptr(), _stream()),
+                             int(tile_rows), int(v_stride), *last, ctx.status.data_ptr(),
+                             _stream()),
            "chunk_attention")
 
 
@@ -423,10 +439,11 @@ def kv_write_rotated(proj: torch.Tensor, fk: torch.Tensor, rotary_dim: int,
 
 
 def attention_finish(o: torch.Tensor, fv: "torch.Tensor | None", gate: "torch.Tensor | None",
-                     out: torch.Tensor, heads: int, value_dim: int, ctx) -> None:
+                     out: torch.Tensor, heads: int, value_dim: int, ctx,
+                     gate_per_head: bool = False) -> None:
     """out = the heads' results ``o`` (float32 [N, H dv]) turned back by their tokens' positions
     (``fv`` as in ``kv_write_rotated``) and multiplied by sigmoid(``gate``) (of out's dtype, free
-    row stride), where given."""
+    row stride; [N, H dv], or [N, H] with ``gate_per_head``), where given."""
     n = o.shape[0]
     _f32(o, "o")
     _need(o.is_contiguous() and o.shape == (n, heads * value_dim) and out.is_contiguous()
@@ -435,9 +452,92 @@ def attention_finish(o: torch.Tensor, fv: "torch.Tensor | None", gate: "torch.Te
         _f32(fv, "fv")
         _need(value_dim % 2 == 0 and fv.shape == (value_dim // 2,), "attention_finish: fv [dv / 2]")
     if gate is not None:
-        _need(gate.dtype == out.dtype and gate.stride(1) == 1 and gate.shape == o.shape,
-              "attention_finish: gate [N, H dv] of out's dtype")
+        _need(gate.dtype == out.dtype and gate.stride(1) == 1
+              and gate.shape == ((n, heads) if gate_per_head else o.shape),
+              "attention_finish: gate [N, H dv] (or [N, H]) of out's dtype")
     lib = library.load("attention_chunk")
     _check(lib.de_attn_finish(_tag(out.dtype), o.data_ptr(), ctx.positions.data_ptr(), _ptr(fv),
                               _ptr(gate), gate.stride(0) if gate is not None else 0,
-                              out.data_ptr(), n, heads, value_dim, _stream()), "attention_finish")
+                              out.data_ptr(), n, heads, value_dim, int(gate_per_head), _stream()),
+           "attention_finish")
+
+
+def qkv_prepare(proj: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
+                value_dim: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
+                block_table: torch.Tensor, ctx, bias: "torch.Tensor | None" = None,
+                taps: "torch.Tensor | None" = None, kept: "tuple | None" = None,
+                norm: "tuple | None" = None, rotation: "tuple | None" = None,
+                temperature: "tuple | None" = None, mix: "tuple | None" = None) -> None:
+    """From the stacked projection ``proj`` = [q (H dk) | k (G dk) | v (G dv) | ...] to the
+    queries ``q_out`` [N, H dk] and the keys and values in the pages, through (each optional, in
+    this order): ``bias`` float32 [C] (C = (H + G) dk + G dv); ``taps`` float32 [C, K], a causal
+    convolution over time whose inputs before the step come from ``kept`` = (state [slots, n],
+    offset), laid out as ``conv_state`` leaves them; ``norm`` = (mode, q weight, k weight, eps),
+    mode "head" (weights [dk]) or "whole" (weights [H dk], [G dk]); ``rotation`` = (freq
+    [rot / 2], magnitude, adjacent); ``temperature`` = (coef, every) on q; ``mix`` = ("give",
+    v_first) or ("take", v_first, lambda [1]) with v_first float32 [N, G dv]."""
+    n = proj.shape[0]
+    channels = (heads + kv_heads) * key_dim + kv_heads * value_dim
+    _need(proj.stride(1) == 1 and proj.shape[1] >= channels and proj.dtype == k_pages.dtype
+          == v_pages.dtype == q_out.dtype and q_out.is_contiguous()
+          and q_out.shape == (n, heads * key_dim), "qkv_prepare: proj, q_out [N, H dk] and pages")
+    _need(k_pages.is_contiguous() and v_pages.is_contiguous() and k_pages.dim() == 4
+          and tuple(k_pages.shape[1:]) == (kv_heads, k_pages.shape[2], key_dim)
+          and tuple(v_pages.shape) == (*k_pages.shape[:3], value_dim),
+          "qkv_prepare: pages must be [pages, kv_heads, page, dk] and [..., dv]")
+    _i32(block_table, "block_table")
+    if bias is not None:
+        _f32(bias, "bias")
+        _need(bias.shape == (channels,) and bias.is_contiguous(), "qkv_prepare: bias [C]")
+    conv = (None, 0, None, 0, 0)
+    if taps is not None:
+        _f32(taps, "taps")
+        _need(taps.dim() == 2 and taps.shape[0] == channels and taps.is_contiguous(),
+              "qkv_prepare: taps [C, K]")
+        k = taps.shape[1]
+        conv = (taps.data_ptr(), k, None, 0, 0)
+        if k > 1:
+            state, offset = kept
+            _f32(state, "state")
+            _need(state.dim() == 2 and offset + (k - 1) * channels <= state.shape[1],
+                  "qkv_prepare: the state rows are too short for the convolution's inputs")
+            conv = (taps.data_ptr(), k, state.data_ptr(), state.stride(0), offset)
+    normed = (0, None, None, 0.0)
+    if norm is not None:
+        mode, qw, kw, eps = norm
+        _need(mode in ("head", "whole"), "qkv_prepare: norm over a head or the whole projection")
+        _f32(qw, "q weight"), _f32(kw, "k weight")
+        shapes = ((key_dim,), (key_dim,)) if mode == "head" else ((heads * key_dim,),
+                                                                   (kv_heads * key_dim,))
+        _need((tuple(qw.shape), tuple(kw.shape)) == shapes and qw.is_contiguous()
+              and kw.is_contiguous(), "qkv_prepare: the norm's weights do not fit its mode")
+        normed = (1 if mode == "head" else 2, qw.data_ptr(), kw.data_ptr(), float(eps))
+    turned = (None, 0, 1.0, 0)
+    if rotation is not None and rotation[0].numel() > 0:
+        freq, magnitude, adjacent = rotation
+        _f32(freq, "freq")
+        _need(freq.dim() == 1 and 2 * freq.shape[0] <= key_dim and freq.is_contiguous(),
+              "qkv_prepare: freq [rot / 2], rot at most the key size")
+        turned = (freq.data_ptr(), 2 * freq.shape[0], float(magnitude), int(bool(adjacent)))
+    temp = (0.0, 0) if temperature is None else (float(temperature[0]), int(temperature[1]))
+    mixed = (0, None, None)
+    if mix is not None:
+        v_first = mix[1]
+        _f32(v_first, "v_first")
+        _need(v_first.is_contiguous() and v_first.shape == (n, kv_heads * value_dim),
+              "qkv_prepare: v_first [N, G dv]")
+        if mix[0] == "take":
+            _f32(mix[2], "lambda")
+            mixed = (2, mix[2].data_ptr(), v_first.data_ptr())
+        else:
+            _need(mix[0] == "give", "qkv_prepare: mix gives or takes")
+            mixed = (1, None, v_first.data_ptr())
+    lib = library.load("attention_chunk")
+    _check(lib.de_qkv_prepare(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), q_out.data_ptr(),
+                              ctx.positions.data_ptr(), ctx.token_seq.data_ptr(),
+                              ctx.token_slot.data_ptr(), ctx.seq_pos0.data_ptr(), _ptr(bias),
+                              *conv, *normed, *turned, *temp, *mixed, heads, kv_heads, key_dim,
+                              value_dim, k_pages.data_ptr(), v_pages.data_ptr(),
+                              block_table.data_ptr(), block_table.stride(0), k_pages.shape[2],
+                              k_pages.shape[0], n, ctx.status.data_ptr(), _stream()),
+           "qkv_prepare")

@@ -1,4 +1,4 @@
-from . import llama, sebilorn, vapelix, vomotar  # noqa: F401  (register the architectures)
+from . import bizetar, llama, sebilorn, vapelix, vomotar  # noqa: F401  (register the architectures)
 from .decoder import DecoderModel, expected_tensors
 from .loading import load_model
 

@@ -26,7 +26,8 @@ def _layer_parts(spec: LayerSpec, dtype: torch.dtype, device: torch.device) -> B
     if spec.side_input is not None:
         side_input = build_side_input(spec.side_input, dtype, device)
     return build_block(spec.block, build_mixer(spec.mixer, dtype, device), feed_forward,
-                       build_norm(spec.norm, dtype, device), feed_forward_norm, side_input)
+                       build_norm(spec.norm, dtype, device), feed_forward_norm, side_input,
+                       dict(spec.block_params))
 
 
 def _full_name(prefix: str, local: str) -> str:
@@ -50,6 +51,10 @@ class DecoderModel:
                                  f"{entry.reads_cache_of}, which does not run before it")
         self.blocks = [_layer_parts(spec, dtype, self.device) for spec in self.specs]
         self.final_norm = build_norm(config.final_norm(), dtype, self.device)
+        first = config.embedding_norm()
+        self.embedding_norm = None if first is None else build_norm(first, dtype, self.device)
+        # the states of the stream that blocks read besides the stream itself
+        self.history_depth = max((block.history_depth() for block in self.blocks), default=0)
         self.embedding: "torch.Tensor | None" = None
         self.output: "torch.Tensor | None" = None
 
@@ -69,10 +74,14 @@ class DecoderModel:
                     expected[full] = tuple(shape)
                     if kind == "vector":
                         vectors.add(full)
-        for local, (shape, kind) in self.final_norm.tensors().items():
-            expected[names["final_norm"] + local] = tuple(shape)
-            if kind == "vector":
-                vectors.add(names["final_norm"] + local)
+        outer = [(self.final_norm, names["final_norm"])]
+        if self.embedding_norm is not None:
+            outer.append((self.embedding_norm, names["embedding_norm"]))
+        for norm, prefix in outer:
+            for local, (shape, kind) in norm.tensors().items():
+                expected[prefix + local] = tuple(shape)
+                if kind == "vector":
+                    vectors.add(prefix + local)
         expected[names["output"]] = (self.config.vocabulary, self.config.width)
         # a tied output needs no tensor of its own, unless it goes by the embedding's name
         optional = ({names["output"]} - {names["embedding"]}) if self.config.tied_output else set()
@@ -82,6 +91,8 @@ class DecoderModel:
         """The kernel libraries every step of this model uses: the row-wise kernels, the product
         of its dtype for steps of few tokens, and what its parts name."""
         modules = ["core", "gemm_f32" if self.dtype == torch.float32 else "linear_small"]
+        if self.embedding_norm is not None:
+            modules.append("sublayer")
         for block in self.blocks:
             for part in block.parts().values():
                 for module in part.kernel_modules():
@@ -102,6 +113,9 @@ class DecoderModel:
                            for local in part.tensors()})
         self.final_norm.load({local: tensors[names["final_norm"] + local]
                               for local in self.final_norm.tensors()})
+        if self.embedding_norm is not None:
+            self.embedding_norm.load({local: tensors[names["embedding_norm"] + local]
+                                      for local in self.embedding_norm.tensors()})
         if names["output"] in tensors:
             self.output = compute_matrix(tensors[names["output"]], self.dtype, self.device)
         else:
@@ -160,6 +174,15 @@ class DecoderModel:
         resid = ctx.buffer("model.residual", (ctx.n_tokens, self.config.width), torch.float32)
         ops.embed_rows(ctx.token_ids, self.embedding, resid, self.config.embedding_scale)
         stream = ResidualStream(resid)
+        if self.embedding_norm is not None:
+            self.embedding_norm.normalize_stream(stream, ctx)
+        if self.history_depth:
+            if len(self.plan) + 1 > self.history_depth:
+                raise RuntimeError("the plan runs more layers than its blocks keep states for")
+            stream.history = ctx.buffer("model.history", (self.history_depth, ctx.n_tokens,
+                                                          self.config.width), torch.float32)
+            stream.history[0].copy_(resid)
+            stream.history_count = 1
         first = None
         if any(entry.adds_embedding for entry in self.plan):
             first = ctx.buffer("model.embedding", (ctx.n_tokens, self.config.width),

@@ -1,5 +1,5 @@
 from . import (attention, block, chunk_attention, experts, latent_attention,  # noqa: F401
-               mlp, norm, parallel, recurrent, rope, token_side,
+               mlp, norm, parallel, recurrent, rope, sink_attention, token_side,
                window_attention)  # (register the built-in kinds)
 from .base import (Block, FeedForward, Mixer, Norm, PagedKVSpec, Part, PositionEncoding,
                    StateSpec, build_block, build_feed_forward, build_mixer, build_norm,

@@ -176,6 +176,11 @@ class Block:
                  "side_input": self.side_input}
         return {role: part for role, part in parts.items() if part is not None}
 
+    def history_depth(self) -> int:
+        """How many states of the stream (the embedding rows, then every layer run's result) this
+        block reads besides the stream itself; the model keeps them in ``stream.history``."""
+        return 0
+
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
                 following: "tuple[Norm, Part] | None" = None) -> None:
         """``following``: the norm and the part that read the stream after this block (the next
@@ -255,12 +260,15 @@ def build_side_input(spec: PartSpec, dtype: torch.dtype, device: torch.device) -
 
 
 def build_block(kind: str, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                feed_forward_norm: Norm, side_input: "SideInput | None" = None) -> Block:
+                feed_forward_norm: Norm, side_input: "SideInput | None" = None,
+                params: "dict | None" = None) -> Block:
+    """``params``: the arrangement's own constructor arguments (``LayerSpec.block_params``)."""
     if kind not in BLOCKS:
         raise ValueError(f"unknown block kind '{kind}'; registered: {sorted(BLOCKS)}")
+    params = params or {}
     if side_input is None:
-        return BLOCKS[kind](mixer, feed_forward, mixer_norm, feed_forward_norm)
-    return BLOCKS[kind](mixer, feed_forward, mixer_norm, feed_forward_norm, side_input)
+        return BLOCKS[kind](mixer, feed_forward, mixer_norm, feed_forward_norm, **params)
+    return BLOCKS[kind](mixer, feed_forward, mixer_norm, feed_forward_norm, side_input, **params)
 
 
 def compute_matrix(tensor: torch.Tensor, dtype: torch.dtype, device: torch.device) -> torch.Tensor:

@@ -2,12 +2,18 @@
 (src/models/llama.py:66-89).  The sums are carried as the stream's pending branch and folded in
 by the next norm.  A layer without a feed-forward is the first half only.
 
-``parallel_norms``: both branches read the same x (see ``ParallelNormsBlock``)."""
+``parallel_norms``: both branches read the same x (see ``ParallelNormsBlock``).
+
+``sublayer_norm``: the norm stands on a sublayer's output, the sublayers read x itself, with an
+optional gate on every sublayer's result and an optional average over the depth (see
+``SublayerNormBlock``)."""
 
 from __future__ import annotations
 
+import torch
+
 from ..kernels import ops
-from .base import Block, register_block
+from .base import Block, Part, register_block
 from .context import CacheBinding, ResidualStream, StepContext
 
 
@@ -90,3 +96,132 @@ class ParallelNormsBlock(Block):
 
 
 register_block("parallel_norms", ParallelNormsBlock)
+
+
+class ResidualGate(Part):
+    """sigmoid(W x + b) on a sublayer's result, W [width, width] and b [width] under the names
+    "" and ".b" of the part's prefix.  The block runs the product on the sublayer's input and
+    hands the rest to the kernel that also norms and adds."""
+
+    def __init__(self, width: int, dtype: torch.dtype, device: torch.device) -> None:
+        super().__init__(dtype, device)
+        self.width = width
+        self.weight = self.bias = None
+
+    def tensors(self):
+        return {"": ((self.width, self.width), "matrix"), ".b": ((self.width,), "bias")}
+
+    def load(self, tensors):
+        self.weight = tensors[""].to(device=self.device, dtype=self.dtype).contiguous()
+        self.bias = tensors[".b"].to(device=self.device, dtype=torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ("sublayer",)
+
+
+class DepthMix(Part):
+    """The learned weights c [count] with which the stream that leaves a layer is mixed from the
+    embedding rows and every layer's result so far, x = sum_j c[j] X_j."""
+
+    def __init__(self, count: int, dtype: torch.dtype, device: torch.device,
+                 tensor: str = "dwa") -> None:
+        super().__init__(dtype, device)
+        self.count, self.tensor = count, tensor
+        self.coef = None
+
+    def tensors(self):
+        return {self.tensor: ((self.count,), "vector")}
+
+    def load(self, tensors):
+        self.coef = tensors[self.tensor].to(device=self.device, dtype=torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ("sublayer",)
+
+
+class SublayerNormBlock(Block):
+    """x <- x + norm1(mixer(x)); x <- x + norm2(feed_forward(x)): the sublayers read the stream
+    itself (its rounding to the activation dtype), the RMS norms stand on their results.
+
+    ``gated``: a sublayer's result is first multiplied by sigmoid(W x + b) of the same input x
+    (``ResidualGate``; roles "mixer_gate" and "feed_forward_gate").  ``depth``: the layer's result
+    X_(i+1) is kept beside the embedding rows X_0 and the earlier layers' results, and what goes on
+    to the next layer is sum_j c[j] X_j over all ``depth`` of them (``DepthMix``, role
+    "depth_mix"); 0: the layer's result goes on as it is.
+
+    Gate, norm and sum are one kernel a sublayer, float32 throughout; it also leaves the new
+    stream's rounding for the next products (``stream.rows``).  A layer without a feed-forward is
+    the first half only."""
+
+    def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, side_input=None,
+                 gated: bool = False, depth: int = 0) -> None:
+        super().__init__(mixer, feed_forward, mixer_norm, feed_forward_norm, side_input)
+        if side_input is not None:
+            raise ValueError("sublayer_norm: this arrangement takes no side input")
+        for norm in (mixer_norm, feed_forward_norm):
+            if norm is not None and (getattr(norm, "groups", 1) != 1
+                                     or not hasattr(norm, "eps") or hasattr(norm, "bias")):
+                raise ValueError("sublayer_norm: the norms on the sublayers' results are RMS "
+                                 "norms over the whole row")
+        width, dtype, device = mixer_norm.width, mixer.dtype, mixer.device
+        self.mixer_gate = ResidualGate(width, dtype, device) if gated else None
+        self.feed_forward_gate = (ResidualGate(width, dtype, device)
+                                  if gated and feed_forward is not None else None)
+        self.depth_mix = DepthMix(depth, dtype, device) if depth else None
+
+    def history_depth(self) -> int:
+        return self.depth_mix.count if self.depth_mix is not None else 0
+
+    def parts(self):
+        parts = super().parts()
+        for role in ("mixer_gate", "feed_forward_gate", "depth_mix"):
+            if getattr(self, role) is not None:
+                parts[role] = getattr(self, role)
+        return parts
+
+    def _join(self, y, gate, norm, h, stream, ctx, out, rows):
+        """out = stream + norm(y * gate(h)); ``rows``: where its rounding goes (or None)."""
+        if gate is None:
+            raise NotImplementedError("sublayer_norm: only the gated form has a kernel")
+        z = ctx.buffer("block.gate", (h.shape[0], gate.width))
+        ops.linear(h, gate.weight, out=z, status=ctx.status)
+        ops.gated_normed_add(y, z, gate.bias, norm.weight, norm.eps, stream.resid, out, rows)
+
+    def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
+                following=None) -> None:
+        if stream.ahead is not None or stream.pending is not None:
+            raise RuntimeError("a block whose sublayers read the stream itself takes a stream "
+                               "with nothing pending")
+        resid = stream.resid
+        wide = ctx.dtype == torch.float32
+        shape = tuple(resid.shape)
+        rows = None if wide else ctx.buffer("block.rows", shape)
+        h = resid if wide else stream.rows
+        if h is None:                                  # the stream came without its rounding
+            h = rows
+            h.copy_(resid)
+        result = resid
+        if self.depth_mix is not None:
+            if stream.history is None or stream.history.shape[0] < self.depth_mix.count:
+                raise RuntimeError("the model keeps no history of the stream for this layer "
+                                   "(Block.history_depth)")
+            if stream.history_count + 1 != self.depth_mix.count:
+                raise RuntimeError(f"this layer mixes {self.depth_mix.count} states of the "
+                                   f"stream, {stream.history_count + 1} exist")
+            result = stream.history[self.depth_mix.count - 1]
+        last = self.feed_forward is None
+        y = self.mixer.forward(h, ctx, cache)
+        self._join(y, self.mixer_gate, self.mixer_norm, h, stream, ctx,
+                   result if last else resid, None if (last and self.depth_mix) else rows)
+        if not last:
+            h = resid if wide else rows
+            y = self.feed_forward.forward(h, ctx)
+            self._join(y, self.feed_forward_gate, self.feed_forward_norm, h, stream, ctx, result,
+                       None if self.depth_mix else rows)
+        if self.depth_mix is not None:
+            stream.history_count += 1
+            ops.depth_mix(stream.history[: self.depth_mix.count], self.depth_mix.coef, resid, rows)
+        stream.rows = rows
+
+
+register_block("sublayer_norm", SublayerNormBlock)

@@ -165,3 +165,10 @@ class ResidualStream:
         self.resid = resid                      # float32 [N, width]
         self.pending: "torch.Tensor | None" = None
         self.ahead: "NormAhead | None" = None
+        # the stream's rounding to the activation dtype, where the kernel that last wrote the
+        # stream left one (blocks whose sublayers read the stream itself)
+        self.rows: "torch.Tensor | None" = None
+        # the embedding rows and the results of the layers so far, float32 [count, N, width], for
+        # blocks that mix the stream over the depth; ``history_count`` of them are filled
+        self.history: "torch.Tensor | None" = None
+        self.history_count = 0

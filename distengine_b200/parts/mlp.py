@@ -105,5 +105,46 @@ class DenseMLP(FeedForward):
         return out
 
 
+class PolyNormMLP(FeedForward):
+    """down( P( up(x) ) ) whose activation is a learned cubic of normed powers: with N dividing a
+    token's vector of inner values by its root mean square (eps inside the root),
+    P(z) = a N(z) + b N(z^2) + c N(z^3) + e, powers element by element; (a, b, c, e) are the four
+    numbers of the tensor ``coefficients``.  The statistics and the sum are float32."""
+
+    def __init__(self, width: int, inner: int, eps: float, dtype: torch.dtype,
+                 device: torch.device, names: "tuple[str, str]" = ("up", "down"),
+                 coefficients: str = "act") -> None:
+        super().__init__(dtype, device)
+        self.width, self.inner, self.eps = width, inner, float(eps)
+        self.names, self.coefficients = tuple(names), coefficients
+        self.w_up = self.w_down = self.coef = None
+
+    def tensors(self):
+        up, down = self.names
+        return {up: ((self.inner, self.width), "matrix"), down: ((self.width, self.inner), "matrix"),
+                self.coefficients: ((4,), "vector")}
+
+    def load(self, tensors):
+        up, down = self.names
+        self.w_up = compute_matrix(tensors[up], self.dtype, self.device)
+        self.w_down = compute_matrix(tensors[down], self.dtype, self.device)
+        self.coef = tensors[self.coefficients].to(device=self.device,
+                                                  dtype=torch.float32).contiguous()
+
+    def kernel_modules(self):
+        return ("sublayer",)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, ahead=None) -> torch.Tensor:
+        n = x.shape[0]
+        z = ctx.buffer("mlp.up", (n, self.inner))
+        ops.linear(x, self.w_up, out=z, status=ctx.status)
+        act = ctx.buffer("mlp.act", (n, self.inner))
+        ops.poly_norm(z, self.coef, self.eps, act)
+        out = ctx.buffer("mlp.out", (n, self.width))
+        ops.linear(act, self.w_down, out=out, status=ctx.status)
+        return out
+
+
 register_feed_forward("gated_mlp", GatedMLP)
 register_feed_forward("dense_mlp", DenseMLP)
+register_feed_forward("polynorm_mlp", PolyNormMLP)

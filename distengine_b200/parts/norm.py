@@ -60,6 +60,19 @@ class RMSNorm(Norm):
         return out
 
 
+    def normalize_stream(self, stream: ResidualStream, ctx: StepContext) -> None:
+        """The stream itself becomes its norm (float32, in place): the norm of the embedding
+        rows.  Its rounding to the activation dtype is left in ``stream.rows``."""
+        if self.groups != 1 or stream.pending is not None or stream.ahead is not None:
+            raise RuntimeError("rmsnorm: the stream is normed in place over whole rows, with "
+                               "nothing pending")
+        rows = None
+        if self.dtype != torch.float32:
+            rows = ctx.buffer("norm.stream_rows", tuple(stream.resid.shape))
+        ops.norm_stream(stream.resid, self.weight, self.eps, rows)
+        stream.rows = rows
+
+
 class LayerNorm(Norm):
     def __init__(self, width: int, eps: float, dtype: torch.dtype, device: torch.device,
                  tensor: str = "weight", bias: str = "bias") -> None:
