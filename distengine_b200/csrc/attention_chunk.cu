@@ -50,7 +50,17 @@ struct Sight {
     int linear;         // the distance penalty is r1[h] * (i - j) instead of the logarithmic one
     const float* sink;  // [heads] or null: the softmax's denominator also holds exp(sink[h]), a
                         // weight without a key or a value (not scaled, no penalty)
+    const void* gate;   // or null: a row's result is multiplied by sigmoid(gate) before it is
+    int ld_gate;        // stored; gate of the queries' type, rows ld_gate apart, one number a
+    int gate_per_head;  // feature ([heads dv]) or, with gate_per_head, one a head ([heads])
 };
+template <typename T>
+__device__ __forceinline__ float sight_gate(const Sight& s, size_t token, int head, int dv,
+                                            int feature) {
+    if (s.gate == nullptr) return 1.0f;
+    const T* g = (const T*)s.gate + token * s.ld_gate + (s.gate_per_head ? head : head * dv + feature);
+    return 1.0f / (1.0f + expf(-to_float(*g)));
+}
 // 1 / (the row's sum of weights, with the sink's share): m is the row's reference maximum
 __device__ __forceinline__ float sight_inverse(const Sight& s, int head, float m, float l) {
     if (s.sink != nullptr) l += expf(s.sink[head] - m);
@@ -519,7 +529,9 @@ attn_chunk_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ out,
 #pragma unroll
     for (int i = 0; i < MAX_D / 32; ++i) {
         const int dd = lane + 32 * i;
-        if (dd < dv) store_out<T>(out, out_f32, o + dd, acc[i] * inv);
+        if (dd < dv)
+            store_out<T>(out, out_f32, o + dd,
+                         acc[i] * inv * sight_gate<T>(sight, (size_t)(tok0 + t), hq, dv, dd));
     }
 }
 
@@ -754,7 +766,9 @@ attn_chunk_vec_kernel(const T* __restrict__ q, int q_stride, void* __restrict__ 
             if (dd < dv) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
-                    store_out<T>(out, out_f32, o + dd + e, acc[i][b][e] * inv);
+                    store_out<T>(out, out_f32, o + dd + e,
+                                 acc[i][b][e] * inv * sight_gate<T>(sight, (size_t)(tok0 + tok[i]),
+                                                                    hq[i], dv, dd + e));
             }
         }
     }
@@ -1014,7 +1028,9 @@ attn_chunk_tiled_kernel(const T* __restrict__ q, int q_stride, void* __restrict_
             if (col < dv) {
 #pragma unroll
                 for (int x = 0; x < 4; ++x)
-                    store_out<T>(out, out_f32, o + col + x, acc[e][c][x] * inv);
+                    store_out<T>(out, out_f32, o + col + x,
+                                 acc[e][c][x] * inv * sight_gate<T>(sight, (size_t)(tok0 + tok[e]),
+                                                                    hq[e], dv, col + x));
             }
         }
     }
@@ -1328,7 +1344,9 @@ attn_chunk_decode_kernel(const T* __restrict__ q, int q_stride, void* __restrict
 #pragma unroll
         for (int b = 0; b < MAX_D / 32; ++b) {
             const int dd = lane + 32 * b;
-            if (dd < dv) store_out<T>(out, out_f32, o + dd, res[b] * inv);
+            if (dd < dv)
+                store_out<T>(out, out_f32, o + dd,
+                             res[b] * inv * sight_gate<T>(sight, (size_t)tok, h0 + i, dv, dd));
         }
     }
 }
@@ -1398,13 +1416,16 @@ DE_EXPORT int de_attn_chunk_decode(int dtype, const void* q, int q_stride, void*
                                    int page, float scale, int chunk, int window, int keep_first,
                                    float softcap, int out_f32, int fused, const float* fk, int rot,
                                    const float* fv, int write_kv, const void* gate, int ld_gate,
-                                   int v_stride, int linear, const float* sink, int* status,
-                                   void* stream) {
+                                   int v_stride, int linear, const float* sink,
+                                   const void* out_gate, int ld_out_gate, int gate_per_head,
+                                   int* status, void* stream) {
     if (n_seqs <= 0) return 0;
     // v_stride 0: values in rows of their own; else rows of v_pages are that many elements apart
     const int pn_v = dtype == DE_BF16 ? 8 : 4;
     if (v_stride != 0 && (v_stride < dv || v_stride % pn_v != 0 || fused)) return -2;
-    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv, linear, sink};
+    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv, linear, sink,
+                         out_gate, ld_out_gate, gate_per_head};
+    if (out_gate != nullptr && fused) return -2;     // a fused step has its own gate
     const Fuse fuse = {fused, fk, rot, fv, write_kv, gate, ld_gate};
     if (fused && (rot < 0 || rot % 2 || rot > dk || (fv != nullptr && dv % 2) || out_f32)) return -2;
     const int v_in_k = v_pages == k_pages && v_stride == dk;
@@ -1547,12 +1568,14 @@ DE_EXPORT int de_attn_chunk(int dtype, const void* q, int q_stride, void* out, i
                             int heads, int kv_heads, int dk, int dv, int page, float scale,
                             int chunk, int window, int keep_first, float softcap, int out_f32,
                             int tile_rows, int v_stride, int linear, const float* sink,
+                            const void* out_gate, int ld_out_gate, int gate_per_head,
                             int* status, void* stream) {
     if (num_items <= 0) return 0;
     // v_stride 0: values in rows of their own; else rows of v_pages are that many elements apart
     if (v_stride != 0 && (v_stride < dv || (vec_ok(dtype, dk, dv) && v_stride % (dtype == DE_BF16 ? 8 : 4))))
         return -2;
-    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv, linear, sink};
+    const Sight sight = {chunk, window, keep_first, softcap, v_stride ? v_stride : dv, linear, sink,
+                         out_gate, ld_out_gate, gate_per_head};
     if (dk <= 0 || dk > MAX_DK || dv <= 0 || dv > MAX_D || heads % kv_heads != 0) return -2;
     cudaStream_t s = (cudaStream_t)stream;
     if (tile_rows != ROWS && !((tile_rows == ROWS * 4 && vec_fits(dtype, dk, dv)) ||

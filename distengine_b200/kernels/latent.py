@@ -141,13 +141,15 @@ def experts_down(inner: torch.Tensor, down: torch.Tensor, pair_of: torch.Tensor,
                                y.data_ptr(), _stream()), "experts_down")
 
 
-def experts_tensor_ok(h: torch.Tensor, up: torch.Tensor, pairs: int) -> bool:
+def experts_tensor_ok(h: torch.Tensor, up: torch.Tensor, pairs: int,
+                      down: "torch.Tensor | None" = None) -> bool:
     """Whether the experts' products of this step go to the tensor cores (``experts_product``):
     bfloat16 and rows of whole 16-byte pieces.  Steps of few pairs go there too: their tiles of
     128 slots are mostly empty, but the products are bound by the experts' weights, which the
     kernel streams through TMA."""
     return (h.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and pairs >= TENSOR_PAIRS
-            and up.shape[1] % 8 == 0 and up.shape[2] % 8 == 0)
+            and up.shape[1] % 8 == 0 and up.shape[2] % 8 == 0
+            and (down is None or down.shape[2] % 8 == 0))
 
 
 TENSOR_PAIRS = 1

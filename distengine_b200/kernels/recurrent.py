@@ -236,10 +236,19 @@ def mean_of_normed(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch
 
 
 # ------------------------------------------------------------------------------- chunk attention
-def _penalty(r1, r2, heads: int, slopes=None, sink=None):
-    """The penalty's two pointers and the kernels' last arguments (linear, sink): either
-    r1 log(1 + r2 distance) or ``slopes`` [heads] times the distance; ``sink`` [heads]: the
-    softmax's denominator also holds exp(sink)."""
+def _penalty(r1, r2, heads: int, slopes=None, sink=None, gate=None, gate_per_head=False,
+             like=None, value_dim=0):
+    """The penalty's two pointers and the kernels' last arguments (linear, sink, gate, its row
+    stride, whether it is one number a head): either r1 log(1 + r2 distance) or ``slopes``
+    [heads] times the distance; ``sink`` [heads]: the softmax's denominator also holds exp(sink);
+    ``gate`` [N, heads dv] (or [N, heads] with ``gate_per_head``) of the queries' dtype ``like``:
+    a row's result is multiplied by sigmoid(gate) before it is stored."""
+    gated = (None, 0, 0)
+    if gate is not None:
+        _need(gate.dtype == like and gate.stride(1) == 1 and gate.dim() == 2
+              and gate.shape[1] == (heads if gate_per_head else heads * value_dim),
+              "attention: gate [N, heads dv] or [N, heads] of the queries' dtype")
+        gated = (gate.data_ptr(), gate.stride(0), int(bool(gate_per_head)))
     _need((r1 is None) == (r2 is None), "attention: r1 and r2 come together")
     _need(r1 is None or slopes is None, "attention: one distance penalty, not two")
     if r1 is not None:
@@ -250,8 +259,8 @@ def _penalty(r1, r2, heads: int, slopes=None, sink=None):
             _f32(t, name)
             _need(t.shape == (heads,) and t.is_contiguous(), f"attention: {name} [heads]")
     if slopes is not None:
-        return slopes, slopes, (1, _ptr(sink))
-    return r1, r2, (0, _ptr(sink))
+        return slopes, slopes, (1, _ptr(sink), *gated)
+    return r1, r2, (0, _ptr(sink), *gated)
 
 
 def chunk_rows_per_tile(dtype: torch.dtype, key_dim: int, value_dim: int, wide: bool,
@@ -296,7 +305,9 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
                            keep_first: int = 0, softcap: float = 0.0,
                            fused: "dict | None" = None, v_stride: int = 0,
                            slopes: "torch.Tensor | None" = None,
-                           sink: "torch.Tensor | None" = None) -> None:
+                           sink: "torch.Tensor | None" = None,
+                           gate: "torch.Tensor | None" = None,
+                           gate_per_head: bool = False) -> None:
     """``chunk_attention`` for a step in which every sequence brings one token: a block a
     (sequence, kv head), its warps share the key tiles out; no work items.
 
@@ -314,7 +325,7 @@ def chunk_attention_decode(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Te
           and out.shape[1] == heads * value_dim and q.shape[0] == ctx.n_seqs,
           "chunk_attention_decode: q, out and pages; one token a sequence")
     _i32(block_table, "block_table")
-    r1, r2, last = _penalty(r1, r2, heads, slopes, sink)
+    r1, r2, last = _penalty(r1, r2, heads, slopes, sink, gate, gate_per_head, q.dtype, value_dim)
     extra = (0, None, 0, None, 0, None, 0)
     if fused is not None:
         fk, rot, fv, gate = fused["fk"], fused["rotary_dim"], fused["fv"], fused["gate"]
@@ -378,7 +389,8 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
                     value_dim: int, scale: float, chunk: int, ctx, tile_rows: int = 8,
                     window: int = 0, keep_first: int = 0, softcap: float = 0.0,
                     v_stride: int = 0, slopes: "torch.Tensor | None" = None,
-                    sink: "torch.Tensor | None" = None) -> None:
+                    sink: "torch.Tensor | None" = None, gate: "torch.Tensor | None" = None,
+                    gate_per_head: bool = False) -> None:
     """Attention of the step's rows over the pages: q rows of [heads dk] at the front of ``q``
     (row stride free), out [N, heads dv]; ``tile_rows``: the rows of a tile that ``items`` were
     cut for (``chunk_rows_per_tile``); ``v_stride`` as in ``chunk_attention_decode``; see
@@ -387,7 +399,7 @@ def chunk_attention(q: torch.Tensor, out: torch.Tensor, k_pages: torch.Tensor,
           and out.dtype in (q.dtype, torch.float32)
           and out.shape[1] == heads * value_dim, "chunk_attention: q, out and pages")
     _i32(block_table, "block_table"), _i32(items, "items")
-    r1, r2, last = _penalty(r1, r2, heads, slopes, sink)
+    r1, r2, last = _penalty(r1, r2, heads, slopes, sink, gate, gate_per_head, q.dtype, value_dim)
     lib = library.load("attention_chunk")
     _check(lib.de_attn_chunk(_tag(q.dtype), q.data_ptr(), q.stride(0), out.data_ptr(),
                              out.stride(0), k_pages.data_ptr(), v_pages.data_ptr(),

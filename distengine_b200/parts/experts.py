@@ -79,7 +79,7 @@ class RoutedExperts(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, ahead=None) -> torch.Tensor:
         n, top = x.shape[0], self.top
-        tensor = lk.experts_tensor_ok(x, self.up, n * top)
+        tensor = lk.experts_tensor_ok(x, self.up, n * top, self.down)
         segment = lk.SEGMENT_TENSOR if tensor else lk.SEGMENT
         tiles = lk.experts_tiles(n, top, self.experts, segment)
         chosen = ctx.buffer("experts.chosen", (n, top), torch.int32)

@@ -214,20 +214,20 @@ class SinkAttention(ProjectedMixer):
             mix=mix)
         if state is not None:
             rk.conv_state(proj, state.state, 0, self.channels, self.taps, ctx)
-        raw = ctx.buffer("sink_attention.raw", (n, H * dv), torch.float32)
-        if ctx.notes[self.key] == 0:
-            rk.chunk_attention_decode(q, raw, pages.k_pages, pages.v_pages, pages.block_table,
-                                      None, None, H, G, dk, dv, self.scale, 0, ctx,
-                                      slopes=self.slopes, sink=self.sink)
-        else:
-            rk.chunk_attention(q, raw, pages.k_pages, pages.v_pages, pages.block_table,
-                               ctx.arrays[self.key + "/items"], None, None, H, G, dk, dv,
-                               self.scale, 0, ctx, tile_rows=ctx.notes[self.key],
-                               slopes=self.slopes, sink=self.sink)
+        # the gate rides in the attention kernels' last step: the heads' results are multiplied
+        # in float32 and rounded once
         context = ctx.buffer("sink_attention.context", (n, H * dv))
         gate = proj[:, self.g_col: self.g_col + self._gate_rows()] if self.gate else None
-        rk.attention_finish(raw, None, gate, context, H, dv, ctx,
-                            gate_per_head=self.gate == "head")
+        extras = dict(slopes=self.slopes, sink=self.sink, gate=gate,
+                      gate_per_head=self.gate == "head")
+        if ctx.notes[self.key] == 0:
+            rk.chunk_attention_decode(q, context, pages.k_pages, pages.v_pages,
+                                      pages.block_table, None, None, H, G, dk, dv, self.scale, 0,
+                                      ctx, **extras)
+        else:
+            rk.chunk_attention(q, context, pages.k_pages, pages.v_pages, pages.block_table,
+                               ctx.arrays[self.key + "/items"], None, None, H, G, dk, dv,
+                               self.scale, 0, ctx, tile_rows=ctx.notes[self.key], **extras)
         return self.project_out(context, "sink_attention.out", ctx, ahead, out_dtype=out_dtype)
 
 

@@ -145,8 +145,8 @@ class RoutingTap:
         self._module, self._route, self._step = lk, lk.experts_route, self.runner.step
         calls: list = []
 
-        def route(h, router, bias, top, chosen, weight):
-            self._route(h, router, bias, top, chosen, weight)
+        def route(h, router, bias, top, chosen, weight, *more):
+            self._route(h, router, bias, top, chosen, weight, *more)
             calls.append(chosen.clone())
 
         def step(entries, extra=None):
