@@ -66,7 +66,8 @@ def _run_in_portions(mixers, h, xs, portions):
         x = torch.cat([xs[rid][fed[rid]: fed[rid] + n] for rid, n in entries]).to(DEV)
 
         def run(ctx, bindings):
-            return torch.stack([m.forward(x, ctx, b).float() for m, b in zip(mixers, bindings)])
+            return torch.stack([m.forward(x, ctx, b).float().clone()
+                                for m, b in zip(mixers, bindings)])
 
         out = h.run(entries, run).cpu()
         at = 0
@@ -163,21 +164,26 @@ def test_values_are_mixed_between_layers():
 @pytest.mark.parametrize("decoded", [0, 40])
 @pytest.mark.parametrize("far", [0, 1, 15, 16, 17, 200])
 def test_one_key_among_hundreds_decides(kind, far, decoded):
-    """The key and query matrices are made equal and the scale sharp, and the last token's input
-    is the far token's: that key (the first token, one at a page border, one far back) carries the
-    last token's softmax if it is seen, at the right distance and turned by the right position; a
-    lost or misplaced key changes the result."""
-    width, T = 40, 420
+    """The query matrix reads one half of the input as the key matrix reads the other, and the
+    last token's first half is the far token's second: that key (the first token, one at a page
+    border, one far back) carries the last token's softmax if it is seen, at the right distance
+    and turned by the right position, and its value is its own; a lost or misplaced key changes
+    the result."""
+    width, T, dk = 40, 420, 32
     if kind == "attention":
-        entry = bc.layer(kind, bc.first(4, 1, 8, 12, 24.0, q_temp=(0.5, 128)), None)
+        entry = bc.layer(kind, bc.first(4, 1, dk, 12, 1.0, q_temp=(0.5, 128)), None)
     else:
-        entry = bc.layer(kind, bc.second(4, 1, 8, 12, 3.0, rot=(10000.0, 2, (8.0, 64, 32.0, 1.0))),
-                         None)
+        entry = bc.layer(kind, bc.second(4, 1, dk, 12, 1.0,
+                                         rot=(10000.0, 4, (8.0, 64, 32.0, 1.0))), None)
     config = _model(width, [entry])
     from distengine_b200.config.bizetar import BizetarConfig
     from distengine_b200.parts import build_mixer
     weights = pb.random_weights(config, 31, spread=2.0)
-    weights["l0.mix.q"] = weights["l0.mix.k"].repeat(4, 1)         # every head asks for its like
+    half = width // 2
+    wq = torch.zeros(dk, width)
+    wq[:, :half] = weights["l0.mix.k"][:, half:]
+    weights["l0.mix.k"][:, :half] = 0
+    weights["l0.mix.q"] = wq.repeat(4, 1)                          # every head asks for its like
     if kind == "attention":
         weights["l0.mix.q.norm"] = weights["l0.mix.k.norm"].repeat(4)
         weights["l0.mix.sink"] = torch.full((4,), 2.0)
@@ -189,15 +195,19 @@ def test_one_key_among_hundreds_decides(kind, far, decoded):
     mixer.load({local: weights[f"l0.mix.{local}"] for local in mixer.tensors()})
     wd = {k: v.double() for k, v in weights.items()}
     fn = pb.attention if kind == "attention" else pb.attention_2
-    g = _gen(100 * far + 1)
-    x = torch.randn(T, width, generator=g)
-    x[T - 1] = x[far]
-    want, _ = fn(x.double(), wd, "l0.mix.", entry["mixer"], 1e-5, None)
-    # that the key carries weight at the last token shows in what another input there gives
-    other = x.clone()
-    other[far] = torch.randn(width, generator=g)
-    moved, _ = fn(other.double(), wd, "l0.mix.", entry["mixer"], 1e-5, None)
-    assert (want[T - 1] - moved[T - 1]).abs().max() > 0.05 * want[T - 1].abs().max()
+    for seed in range(40):
+        g = _gen(100 * far + seed)
+        x = torch.randn(T, width, generator=g)
+        x[T - 1, :half] = x[far, half:]
+        want, _ = fn(x.double(), wd, "l0.mix.", entry["mixer"], 1e-5, None)
+        # that the key carries weight at the last token shows in what another input there gives
+        other = x.clone()
+        other[far] = torch.randn(width, generator=g)
+        moved, _ = fn(other.double(), wd, "l0.mix.", entry["mixer"], 1e-5, None)
+        if (want[T - 1] - moved[T - 1]).abs().max() > 0.3 * want[T - 1].abs().max():
+            break
+    else:
+        raise AssertionError("no input was found whose key decides")
     h = PartHarness([mixer], [mixer.cache_spec()], torch.float32, page_size=16, num_pages=28)
     head = T - decoded
     portions = [[("a", head - 150)], [("a", 150)]] + [[("a", 1)]] * decoded
