@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload headline|mixed|long|fp32|vomotar|sebilorn|vapelix] [--layers L]
+                    [--workload headline|mixed|long|fp32|vomotar|sebilorn|vapelix|bizetar] [--layers L]
 
 The default (``headline``) has the TinyLlama-1.1B layer sizes in bfloat16.  A step is one decode
 step of a batch of 8 requests whose prompts of 512 tokens are in the cache; K steps are timed with
@@ -45,6 +45,13 @@ Other workloads, each with its own line (the number of layers is named beside th
   one input a layer) at the same width and vocabulary, beside Llama with the same number of
   layers: decode at batch 8 and 64 and a prompt of 2,048 tokens, and every kernel of the design
   alone against its roofline, each beside the like kernel of the other models.
+* ``bizetar``: the Bizetar architecture (attention with a sink in two forms - biases, a short
+  convolution, norms per head and stretched rotation, or norms over the projection, a distance
+  bias and a growing query -, norms on the gated results of the sublayers, a stream mixed over the
+  depth, a cubic activation, gated experts beside router outputs that hand the input on) at the
+  same width and vocabulary, beside Sebilorn and Llama with the same number of layers: decode at
+  batch 8 and 64 and a prompt of 2,048 tokens, and every kernel of the design alone against its
+  roofline, each beside the like kernel of the other models.
 """
 
 from __future__ import annotations
@@ -1131,6 +1138,326 @@ def workload_vapelix(args, warmup: int, steps: int) -> int:
     return 0
 
 
+def bizetar_shape(layers: int) -> dict:
+    """A Bizetar model of the headline's width and vocabulary: 16 query heads on 4 key/value heads
+    of 128 features (keys and values) in every layer; three layers in four are the form with
+    biases, a convolution of 3 taps, norms per head and stretched rotation, every fourth the form
+    with norms over the whole projection, a distance bias and a query that grows; a dense
+    feed-forward of the headline's size in every fourth layer and 16 gated experts of 1,024 inner
+    features beside 4 outputs that hand the input on, 4 a token, in the others (about as many
+    active feed-forward weights as the dense layers have).  Every layer mixes values."""
+    rot = {"dims": 128, "base": 50000.0,
+           "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    common = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+              "v_mix": True}
+    second = {"type": "attention_2", "mixer": dict(common, conv=3, rot=rot)}
+    first = {"type": "attention", "mixer": dict(common, q_temp={"coef": 0.5, "every": 128})}
+    dense = {"kind": "dense", "ff": MODEL["intermediate_size"]}
+    routed = {"kind": "moe", "expert": {"ff": 1024},
+              "router": {"experts": 16, "top": 4, "identity": 4}}
+    return {"architecture": "Bizetar", "vocab": MODEL["vocab_size"], "width": MODEL["hidden_size"],
+            "norm": {"eps": 1e-5},
+            "layers": [dict(first if i % 4 == 2 else second, mlp=dense if i % 4 == 0 else routed)
+                       for i in range(layers)]}
+
+
+def bizetar_folder(layers: int) -> str:
+    from distengine_b200.weights import write_random_model
+    folder = os.path.join(tempfile.gettempdir(), f"distengine_b200-bench-{os.getuid()}",
+                          f"bizetar-shape-{layers}-layers-seed0-bf16")
+    marker = os.path.join(folder, ".complete")
+    if not os.path.isfile(marker):
+        print("[bench] writing the random-weights model folder ...", file=sys.stderr, flush=True)
+        write_random_model(bizetar_shape(layers), folder, seed=0, dtype="bfloat16",
+                           norm_init="uniform")
+        with open(marker, "w") as handle:
+            handle.write("ok")
+    return folder
+
+
+def bizetar_kernels(peak: dict) -> list[dict]:
+    """The design's kernels alone at the sizes of ``bizetar_shape``, for a prompt of 2,048 tokens
+    and for a decode step of 64 sequences at position 600, each beside the like kernel of the
+    closest models, measured in the same run (``like``): the attention with sink, distance bias
+    and gate beside the same kernels with a window (Sebilorn's), what prepares q, k and v beside
+    the kernel that turns and stores them, the block's row kernels beside the RMS norm, the cubic
+    activation beside silu * up, the experts' kernels beside their ungated form (Vapelix's)."""
+    from types import SimpleNamespace
+    import numpy as np
+    import torch
+    from distengine_b200.kernels import latent as lk
+    from distengine_b200.kernels import ops
+    from distengine_b200.kernels import recurrent as rk
+    from distengine_b200.kernels.attention_plan import build_plan
+    from distengine_b200.parts.sink_attention import stretched_frequencies
+    from distengine_b200.parts.window_attention import rotary_frequencies
+    dev, bf16 = "cuda:0", torch.bfloat16
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fp32_peak = 148 * 128 * 2 * 1.965e9          # fused multiply-adds of the CUDA cores
+    tensor_peak = peak["bf16_tflops"] * 1e12
+
+    def ctx_of(lens, pos0):
+        lens = np.asarray(lens, dtype=np.int32)
+        pos0 = np.asarray(pos0, dtype=np.int32)
+        qstart = (np.cumsum(lens) - lens).astype(np.int32)
+        seq = np.repeat(np.arange(len(lens), dtype=np.int32), lens)
+        slots = np.arange(len(lens), dtype=np.int32)
+        pos = pos0[seq] + np.arange(lens.sum(), dtype=np.int32) - qstart[seq]
+        d = lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.int32)).to(dev)
+        return SimpleNamespace(n_seqs=len(lens), token_seq=d(seq), token_slot=d(slots[seq]),
+                               positions=d(pos), seq_slot=d(slots), seq_qstart=d(qstart),
+                               seq_qlen=d(lens), seq_pos0=d(pos0),
+                               host=SimpleNamespace(seq_qlen=lens, seq_pos0=pos0),
+                               status=torch.zeros(1, dtype=torch.int32, device=dev))
+
+    def timed(fn, repeats=10):
+        for _ in range(3):
+            fn()
+        times = []
+        for _ in range(repeats):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(times)
+
+    out = []
+
+    def record(name, case, us, bytes_=0, flops=0, tensor_flops=0, like=""):
+        entry = {"kernel": name, "case": case, "us": round(us, 1), "like": like}
+        bounds = {"hbm": bytes_ / (peak["hbm_gbs"] * 1e3), "fp32 fma": flops / fp32_peak * 1e6,
+                  "tensor": tensor_flops / tensor_peak * 1e6}
+        entry["bound"] = max(bounds, key=bounds.get)
+        entry["roofline_us"] = round(bounds[entry["bound"]], 1)
+        entry["frac"] = round(bounds[entry["bound"]] / us, 3)
+        out.append(entry)
+
+    shape = bizetar_shape(4)
+    m, routed = shape["layers"][0]["mixer"], shape["layers"][1]["mlp"]
+    H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    width, ff, page, taps = MODEL["hidden_size"], MODEL["intermediate_size"], PAGE, m["conv"]
+    E, top, eff, idn = (routed["router"]["experts"], routed["router"]["top"],
+                        routed["expert"]["ff"], routed["router"]["identity"])
+    sc = m["rot"]["scaling"]
+    freq, magnitude = stretched_frequencies(m["rot"]["base"], m["rot"]["dims"],
+                                            (sc["factor"], sc["original"], sc["fast"], sc["slow"]))
+    freq = freq.to(dev)
+    C = (H + G) * dk + G * dv
+    w = lambda *s: (torch.randn(*s, device=dev) / s[-1] ** 0.5).to(bf16)
+    f = lambda *s: torch.randn(*s, device=dev)
+    for case, lens, pos0 in (("prompt of 2,048", [2048], [0]), ("decode, 64 sequences", [1] * 64,
+                                                                 [600] * 64)):
+        ctx = ctx_of(lens, pos0)
+        n, s = int(sum(lens)), len(lens)
+        longest = max(p + l for p, l in zip(pos0, lens))
+        pages_seq = (longest + page - 1) // page
+        table = torch.arange(s * pages_seq, dtype=torch.int32, device=dev).view(s, pages_seq)
+        keys = sum(sum(p + i + 1 for i in range(l)) for p, l in zip(pos0, lens))
+        read = sum(p + l for p, l in zip(pos0, lens))
+        # ---- the block's row kernels beside the RMS norm of the other models
+        resid, y = f(n, width), f(n, width).to(bf16)
+        gate_z, bias = f(n, width).to(bf16), f(width)
+        wv = torch.rand(width, device=dev).to(bf16)
+        rows = torch.empty(n, width, dtype=bf16, device=dev)
+        us = timed(lambda: ops.norm_stream(resid, wv, 1e-5, rows))
+        record("norm_stream", case, us, bytes_=n * width * (4 + 4 + 2), like="add_rmsnorm")
+        us = timed(lambda: ops.gated_normed_add(y, gate_z, bias, wv, 1e-5, resid, resid, rows))
+        record("gated_normed_add", case, us, bytes_=n * width * (2 + 2 + 4 + 4 + 2),
+               like="add_rmsnorm")
+        us = timed(lambda: ops.add_rmsnorm(resid, y, wv, 1e-5, rows))
+        record("add_rmsnorm (other models)", case, us, bytes_=n * width * (4 + 4 + 2 + 2))
+        history, coef = f(5, n, width), f(5)
+        us = timed(lambda: ops.depth_mix(history, coef, resid, rows))
+        record("depth_mix (five states)", case, us, bytes_=n * width * (5 * 4 + 4 + 2),
+               like="scaled_sum")
+        a32, b32 = f(n, width), f(n, width)
+        us = timed(lambda: ops.scaled_sum(a32, b32, 0.5, 0.5, rows))
+        record("scaled_sum (other models)", case, us, bytes_=n * width * 10)
+        # ---- the cubic activation beside silu * up
+        up2 = f(n, 2 * ff).to(bf16)
+        act = torch.empty(n, ff, dtype=bf16, device=dev)
+        us = timed(lambda: ops.poly_norm(up2[:, :ff], f(4), 1e-5, act))
+        record("poly_norm", case, us, bytes_=n * ff * 4, like="silu_mul")
+        us = timed(lambda: ops.silu_mul(up2, act))
+        record("silu_mul (other models)", case, us, bytes_=n * ff * 6)
+        # ---- q, k, v between projection and attention
+        kp = f(s * pages_seq, G, page, dk).to(bf16)
+        vp = f(s * pages_seq, G, page, dv).to(bf16)
+        proj = f(n, C + H * dv).to(bf16)
+        q = torch.empty(n, H * dk, dtype=bf16, device=dev)
+        state = torch.zeros(s, (taps - 1) * C, device=dev)
+        v_first, lam = f(n, G * dv), torch.full((1,), 0.3, device=dev)
+        us = timed(lambda: rk.qkv_prepare(
+            proj, q, H, G, dk, dv, kp, vp, table, ctx, bias=f(C), taps=f(C, taps),
+            kept=(state, 0), norm=("head", f(dk), f(dk), 1e-5),
+            rotation=(freq, magnitude, True), mix=("take", v_first, lam)))
+        record("qkv_prepare (biases, 3 taps, norms per head, rotation, mixed values)", case, us,
+               bytes_=n * (C * 2 * (taps if n > s else 1) + H * dk * 2 + G * (dk + dv) * 2
+                           + G * dv * 4) + (s * (taps - 1) * C * 4 if n == s else 0),
+               like="kv_write_rotated")
+        us = timed(lambda: rk.qkv_prepare(
+            proj, q, H, G, dk, dv, kp, vp, table, ctx, norm=("whole", f(H * dk), f(G * dk), 1e-5),
+            temperature=(0.5, 128), mix=("give", v_first)))
+        record("qkv_prepare (norms over the projection, growing query)", case, us,
+               bytes_=n * (C * 2 + H * dk * 2 + G * (dk + dv) * 2 + G * dv * 4),
+               like="kv_write_rotated")
+        us = timed(lambda: rk.conv_keep(proj, state, 0, C, taps, ctx))
+        record("conv_keep", case, us, bytes_=s * (taps - 1) * C * (2 + 4),
+               like="kv_write_rotated")
+        fk = rotary_frequencies(500000.0, dk, (8.0, 1.0, 4.0, 8192)).to(dev)
+        fv = rotary_frequencies(500000.0, dv).to(dev)
+        us = timed(lambda: rk.kv_write_rotated(proj, fk, dk, fv, H, G, dk, dv, kp, vp, table, True,
+                                               ctx))
+        record("kv_write_rotated (other models)", case, us,
+               bytes_=n * (2 * H * dk + 2 * G * (dk + dv)) * 2)
+        # ---- attention: sink, gate in the last step, with and without the distance bias
+        tile = rk.chunk_rows_per_tile(bf16, dk, dv, n > s,
+                                      rk.long_portion_rows(ctx.host.seq_qlen, H, G))
+        plan = build_plan(ctx.host.seq_qlen, ctx.host.seq_pos0, H // G, G, tile, 0, chunk=0)
+        items = torch.from_numpy(plan.items).to(dev)
+        context = torch.empty(n, H * dv, dtype=bf16, device=dev)
+        sink = f(H)
+        slopes = (2.0 ** (-8.0 * torch.arange(1, H + 1) / H)).float().to(dev)
+        gate_f, gate_h = proj[:, C: C + H * dv], proj[:, C: C + H]
+        single = n == s and rk.chunk_decode_ok(bf16, H, G, dk, dv)
+
+        def attend(out_, **extra):
+            if single:
+                return rk.chunk_attention_decode(q, out_, kp, vp, table, None, None, H, G, dk, dv,
+                                                 0.09, 0, ctx, **extra)
+            return rk.chunk_attention(q, out_, kp, vp, table, items, None, None, H, G, dk, dv,
+                                      0.09, 0, ctx, tile_rows=tile, **extra)
+        moved = read * G * (dk + dv) * 2 + n * H * (dk * 2 + dv * 2 + dv * 2)
+        us = timed(lambda: attend(context, sink=sink, gate=gate_f))
+        record("sink_attention (gate a feature)", case, us, bytes_=moved,
+               flops=2 * keys * H * (dk + dv), like="window_attention")
+        us = timed(lambda: attend(context, sink=sink, slopes=slopes, gate=gate_h,
+                                  gate_per_head=True))
+        record("sink_attention (distance bias, gate a head)", case, us, bytes_=moved,
+               flops=2 * keys * H * (dk + dv), like="window_attention")
+        raw = torch.empty(n, H * dv, device=dev)
+        window, keep = 1024, 4
+        us = timed(lambda: attend(raw, window=window, keep_first=keep, softcap=30.0))
+        wkeys = sum(sum(min(p + i + 1, window + keep) for i in range(l))
+                    for p, l in zip(pos0, lens))
+        record("window_attention (other models: window 1,024, soft cap)", case, us,
+               bytes_=sum(min(p + l, window + keep + l) for p, l in zip(pos0, lens))
+               * G * (dk + dv) * 2, flops=2 * wkeys * H * (dk + dv))
+        us = timed(lambda: rk.attention_finish(raw, fv, gate_f, context, H, dv, ctx))
+        record("attention_finish (other models; here part of the attention)", case, us,
+               bytes_=n * H * dv * (4 + 2 + 2))
+        # ---- routed experts: 16 gated experts of 1,024 inner features and 4 outputs that hand on
+        x = f(n, width).to(bf16)
+        router, corr = f(E + idn, width) / width ** 0.5, 0.01 * f(E + idn)
+        up, down = w(E, 2 * eff, width), w(E, width, eff)
+        tensor = lk.experts_tensor_ok(x, up, n * top, down)
+        seg = lk.SEGMENT_TENSOR if tensor else lk.SEGMENT
+        tiles = lk.experts_tiles(n, top, E, seg)
+        chosen = torch.empty(n, top, dtype=torch.int32, device=dev)
+        weight = torch.empty(n, top, device=dev)
+        pair_of = torch.empty(tiles * seg, dtype=torch.int32, device=dev)
+        tile_expert = torch.empty(tiles, dtype=torch.int32, device=dev)
+        slot_of = torch.empty(n * top, dtype=torch.int32, device=dev)
+        both = torch.zeros(tiles * seg, 2 * eff, dtype=bf16, device=dev)
+        inner = torch.empty(tiles * seg, eff, dtype=bf16, device=dev)
+        gathered = torch.empty(tiles * seg, width, dtype=bf16, device=dev)
+        ye = torch.empty(n * top, width, dtype=bf16, device=dev)
+        eo = torch.empty(n, width, device=dev)
+        us = timed(lambda: lk.experts_route(x, router, corr, top, chosen, weight,
+                                            "corrected_scores"))
+        record("experts_route (scores over all outputs, correction)", case, us,
+               bytes_=n * width * 2 + (E + idn) * width * 4, flops=2 * n * (E + idn) * width,
+               like="experts_route")
+        us = timed(lambda: lk.experts_route(x, router[:E].contiguous(), corr[:E].contiguous(), top,
+                                            chosen, weight))
+        record("experts_route (other models)", case, us, bytes_=n * width * 2 + E * width * 4,
+               flops=2 * n * E * width)
+        lk.experts_route(x, router, corr, top, chosen, weight, "corrected_scores")
+        us = timed(lambda: lk.experts_group(chosen, E, pair_of, tile_expert, slot_of, seg))
+        record("experts_group", case, us, bytes_=n * top * 12 + tiles * seg * 4,
+               like="experts_group")
+        pairs = int((chosen < E).sum())
+        weights_read = min(E, pairs) * eff * width * 2
+        if tensor:
+            us = timed(lambda: lk.experts_gather(x, pair_of, top, gathered))
+            record("experts_gather", case, us, bytes_=pairs * width * 4, like="experts_gather")
+            us = timed(lambda: lk.experts_product(gathered, up, pair_of, tile_expert, both, False,
+                                                  None, ctx.status))
+            record("experts gate and up (tensor cores)", case, us,
+                   bytes_=2 * weights_read + pairs * (width + 2 * eff) * 2,
+                   tensor_flops=4 * pairs * width * eff, like="experts up")
+            us = timed(lambda: ops.act_mul(both, inner, "silu"))
+            record("act_mul (silu(gate) * up of the slots)", case, us,
+                   bytes_=tiles * seg * eff * 6, like="silu_mul")
+            us = timed(lambda: lk.experts_product(inner, down, pair_of, tile_expert, ye, True, None,
+                                                  ctx.status))
+            record("experts down (tensor cores)", case, us,
+                   bytes_=weights_read + pairs * (width + eff) * 2,
+                   tensor_flops=2 * pairs * width * eff, like="experts down")
+            up1 = w(E, eff, width)
+            us = timed(lambda: lk.experts_product(gathered, up1, pair_of, tile_expert, inner, False,
+                                                  "gelu_erf", ctx.status))
+            record("experts up (other models: ungated, tensor cores)", case, us,
+                   bytes_=weights_read + pairs * (width + eff) * 2,
+                   tensor_flops=2 * pairs * width * eff)
+        us = timed(lambda: lk.experts_combine(ye, weight, eo, (chosen, E, x)))
+        record("experts_combine (with the outputs that hand on)", case, us,
+               bytes_=n * width * (top * 2 + 4), like="experts_combine")
+        us = timed(lambda: lk.experts_combine(ye, weight, eo))
+        record("experts_combine (other models)", case, us, bytes_=n * width * (top * 2 + 4))
+    return out
+
+
+def workload_bizetar(args, warmup: int, steps: int) -> int:
+    """Bizetar beside Sebilorn (the closest model: attention with 32-bit scores and weights through
+    the same kernels, a gate on the heads' results) and Llama at equal width, vocabulary and
+    number of layers."""
+    import numpy as np
+    import torch
+    from distengine_b200 import Engine, EngineConfig
+    peak, peak_kind = peaks()
+    layers = args.layers
+    rng = np.random.default_rng(0)
+    vocab = MODEL["vocab_size"]
+    result = {}
+    for name, folder in (("bizetar", bizetar_folder(layers)), ("sebilorn", sebilorn_folder(layers)),
+                         ("llama", model_folder(layers))):
+        pages = (64 * (PROMPT + 8 + warmup + steps) + PREFILL) // PAGE + 64
+        engine = Engine(folder, EngineConfig(dtype="bfloat16", block_size=PAGE, num_blocks=pages,
+                                             decode_batch_size=64, max_batch_tokens=PREFILL,
+                                             max_model_len=4096, use_graphs=not args.no_graphs))
+        entry = {}
+        if args.only != "decode":
+            prefill_ms, prefill_step_ms = timed_prefill(engine, PREFILL, rng, vocab, repeats=5)
+            entry["prefill_2048"] = {"ms": round(prefill_ms, 3),
+                                     "ms_with_host_prepare": round(prefill_step_ms, 3),
+                                     "tokens_per_s": round(PREFILL / prefill_ms * 1e3, 1)}
+        for batch in (8, 64):
+            ms, launches, _, clocks = timed_decode(engine, batch, PROMPT, steps, warmup, rng, vocab)
+            entry[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4),
+                                         "tokens_per_s": round(batch / ms * 1e3, 1),
+                                         "gpu_launches": int(launches), "clocks": clocks}
+        result[name] = entry
+        del engine
+        torch.cuda.empty_cache()
+    mine = result["bizetar"]["decode_b8"]
+    print(json.dumps({
+        "metric": "decode tokens/s at batch 8, Bizetar at the TinyLlama-1.1B width",
+        "value": mine["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+        "warmup": warmup, "ms_per_step": mine["ms_per_step"], "dtype": "bf16",
+        "higher_is_better": True, "data": "synthetic", "impl": "ours", "workload": "bizetar",
+        "config": {"layers": layers, "width": MODEL["hidden_size"],
+                   "ff": MODEL["intermediate_size"], "vocab": vocab, "seq_len": PROMPT,
+                   "page_size": PAGE, "peaks": peak_kind, "shape": bizetar_shape(4)["layers"],
+                   "l2": "weights larger than L2 are read every step; kernels alone: L2 flushed"},
+        "gpu_launches": mine["gpu_launches"], "clocks": mine["clocks"],
+        "models": result, "kernels": [] if args.only == "decode" else bizetar_kernels(peak)}))
+    return 0
+
+
 def workload_long(args, warmup: int, steps: int) -> int:
     """Llama-3-8B layer sizes: 64 requests with prompts of 4,096 tokens (fed as portions of 4,096
     tokens), then decode steps at batch 64 over the long cache; vocabulary 128,256."""
@@ -1333,9 +1660,9 @@ def main() -> int:
                              "DISTENGINE_B200_DEFINES=DE_TRACE)")
     parser.add_argument("--workload", default="headline",
                         choices=["headline", "mixed", "long", "fp32", "vomotar", "sebilorn",
-                                 "vapelix"])
+                                 "vapelix", "bizetar"])
     args = parser.parse_args()
-    if (args.workload in ("mixed", "long", "vomotar", "sebilorn", "vapelix")
+    if (args.workload in ("mixed", "long", "vomotar", "sebilorn", "vapelix", "bizetar")
             and "--layers" not in " ".join(sys.argv)):
         args.layers = 8          # of the 32 that the Llama-2-7B and Llama-3-8B shapes have
 
@@ -1351,7 +1678,8 @@ def main() -> int:
         return {"mixed": workload_mixed, "long": workload_long, "fp32": workload_fp32,
                 "vomotar": workload_vomotar,
                 "sebilorn": workload_sebilorn,
-                "vapelix": workload_vapelix}[args.workload](args, warmup, steps)
+                "vapelix": workload_vapelix,
+                "bizetar": workload_bizetar}[args.workload](args, warmup, steps)
 
     import numpy as np
     import torch

@@ -222,7 +222,7 @@ __global__ void kv_write_rotated_kernel(T* __restrict__ proj, int ld, const int*
 //   taps      a short causal convolution over time on every channel, y_t = sum_j taps[c][j] *
 //             u_(t - K + 1 + j), zeros before the sequence's start; inputs before the step's first
 //             token of the sequence come from the slot's state, kept[i] = projection (without
-//             bias) at position pos0 - (K - 1) + i, as conv_state leaves them
+//             bias) at position pos0 - (K - 1) + i, as conv_keep leaves them
 //   norm      q and k divided by their root mean square (eps inside the root) and weighted: 1 over
 //             every head with weights [dk] that all heads share, 2 over the whole projection with
 //             weights [H dk] and [G dk]
@@ -367,6 +367,30 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __rest
             v_pages[(at + (size_t)h * page) * dv + i] = stored;
         }
     }
+}
+
+// After qkv_prepare: every sequence's slot keeps the last K - 1 rows of the first C columns of
+// proj (the convolution's inputs of the next step), kept[i] = the row at position
+// pos0 + qlen - (K - 1) + i; a portion shorter than K - 1 moves the older rows up.  The layout is
+// the one that the state mixers' convolution keeps (recurrent.cu); a model whose only
+// convolution is this mixer's needs no other library for it.  One block a sequence.
+template <typename T>
+__global__ void conv_keep_kernel(const T* __restrict__ proj, int ld, float* __restrict__ state,
+                                 long long slot_stride, int conv_offset,
+                                 const int* __restrict__ seq_slot,
+                                 const int* __restrict__ seq_qstart,
+                                 const int* __restrict__ seq_qlen, int C, int K) {
+    const int s = blockIdx.x;
+    const int qlen = seq_qlen[s], tok0 = seq_qstart[s];
+    pdl_wait();
+    pdl_trigger();
+    float* kept = state + (size_t)seq_slot[s] * slot_stride + conv_offset;
+    for (int c = threadIdx.x; c < C; c += blockDim.x)
+        for (int i = 0; i < K - 1; ++i) {            // ascending: what is read lies ahead
+            const int rel = qlen - (K - 1) + i;
+            kept[(size_t)i * C + c] = rel >= 0 ? to_float(proj[(size_t)(tok0 + rel) * ld + c])
+                                               : kept[(size_t)(i + qlen) * C + c];
+        }
 }
 
 // After the attention: every head's result (float32 [N, H dv]) turned back by its token's position
@@ -1543,6 +1567,19 @@ DE_EXPORT int de_qkv_prepare(int dtype, const void* proj, int ld, void* q_out,
     if (dtype == DE_BF16) PREP(__nv_bfloat16);
     PREP(float);
 #undef PREP
+}
+
+DE_EXPORT int de_conv_keep(int dtype, const void* proj, int ld, float* state, long long slot_stride,
+                           int conv_offset, const int* seq_slot, const int* seq_qstart,
+                           const int* seq_qlen, int n_seqs, int C, int K, void* stream) {
+    if (n_seqs <= 0 || K <= 1) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DE_BF16)
+        return de_launch(conv_keep_kernel<__nv_bfloat16>, dim3(n_seqs), dim3(256), 0, s,
+                         (const __nv_bfloat16*)proj, ld, state, slot_stride, conv_offset, seq_slot,
+                         seq_qstart, seq_qlen, C, K);
+    return de_launch(conv_keep_kernel<float>, dim3(n_seqs), dim3(256), 0, s, (const float*)proj,
+                     ld, state, slot_stride, conv_offset, seq_slot, seq_qstart, seq_qlen, C, K);
 }
 
 DE_EXPORT int de_attn_finish(int dtype, const float* o, const int* positions, const float* fv,

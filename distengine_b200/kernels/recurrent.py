@@ -474,6 +474,22 @@ def attention_finish(o: torch.Tensor, fv: "torch.Tensor | None", gate: "torch.Te
            "attention_finish")
 
 
+def conv_keep(proj: torch.Tensor, state: torch.Tensor, conv_offset: int, channels: int, taps: int,
+              ctx) -> None:
+    """What ``conv_state`` does, from the attention kernels' library: the slots keep the last
+    ``taps - 1`` rows of the first ``channels`` columns of ``proj`` of every sequence of the
+    step, for ``qkv_prepare`` of the next step."""
+    _f32(state, "state")
+    _need(proj.stride(1) == 1 and proj.shape[1] >= channels and state.dim() == 2
+          and conv_offset + (taps - 1) * channels <= state.shape[1],
+          "conv_keep: the kept rows do not fit")
+    lib = library.load("attention_chunk")
+    _check(lib.de_conv_keep(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), state.data_ptr(),
+                            state.stride(0), conv_offset, ctx.seq_slot.data_ptr(),
+                            ctx.seq_qstart.data_ptr(), ctx.seq_qlen.data_ptr(), ctx.n_seqs,
+                            channels, taps, _stream()), "conv_keep")
+
+
 def qkv_prepare(proj: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: int, key_dim: int,
                 value_dim: int, k_pages: torch.Tensor, v_pages: torch.Tensor,
                 block_table: torch.Tensor, ctx, bias: "torch.Tensor | None" = None,
@@ -484,7 +500,7 @@ def qkv_prepare(proj: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: i
     queries ``q_out`` [N, H dk] and the keys and values in the pages, through (each optional, in
     this order): ``bias`` float32 [C] (C = (H + G) dk + G dv); ``taps`` float32 [C, K], a causal
     convolution over time whose inputs before the step come from ``kept`` = (state [slots, n],
-    offset), laid out as ``conv_state`` leaves them; ``norm`` = (mode, q weight, k weight, eps),
+    offset), laid out as ``conv_keep`` leaves them; ``norm`` = (mode, q weight, k weight, eps),
     mode "head" (weights [dk]) or "whole" (weights [H dk], [G dk]); ``rotation`` = (freq
     [rot / 2], magnitude, adjacent); ``temperature`` = (coef, every) on q; ``mix`` = ("give",
     v_first) or ("take", v_first, lambda [1]) with v_first float32 [N, G dv]."""

@@ -144,7 +144,7 @@ class SinkAttention(ProjectedMixer):
         return self._host_in
 
     def kernel_modules(self):
-        return ("attention_chunk", "recurrent") if self.taps > 1 else ("attention_chunk",)
+        return ("attention_chunk",)
 
     # the norms of a block that reads the stream itself never ride on this mixer's products
     def takes_unscaled(self, n_rows: int) -> bool:
@@ -213,7 +213,7 @@ class SinkAttention(ProjectedMixer):
             rotation=(self.freq, self.magnitude, self.adjacent), temperature=self.temperature,
             mix=mix)
         if state is not None:
-            rk.conv_state(proj, state.state, 0, self.channels, self.taps, ctx)
+            rk.conv_keep(proj, state.state, 0, self.channels, self.taps, ctx)
         # the gate rides in the attention kernels' last step: the heads' results are multiplied
         # in float32 and rounded once
         context = ctx.buffer("sink_attention.context", (n, H * dv))
