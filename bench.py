@@ -1279,7 +1279,8 @@ def bizetar_kernels(peak: dict) -> list[dict]:
         # ---- the cubic activation beside silu * up
         up2 = f(n, 2 * ff).to(bf16)
         act = torch.empty(n, ff, dtype=bf16, device=dev)
-        us = timed(lambda: ops.poly_norm(up2[:, :ff], f(4), 1e-5, act))
+        cubic = f(4)
+        us = timed(lambda: ops.poly_norm(up2[:, :ff], cubic, 1e-5, act))
         record("poly_norm", case, us, bytes_=n * ff * 4, like="silu_mul")
         us = timed(lambda: ops.silu_mul(up2, act))
         record("silu_mul (other models)", case, us, bytes_=n * ff * 6)
@@ -1290,16 +1291,17 @@ def bizetar_kernels(peak: dict) -> list[dict]:
         q = torch.empty(n, H * dk, dtype=bf16, device=dev)
         state = torch.zeros(s, (taps - 1) * C, device=dev)
         v_first, lam = f(n, G * dv), torch.full((1,), 0.3, device=dev)
+        qb, qt, nq, nk, wq, wk = f(C), f(C, taps), f(dk), f(dk), f(H * dk), f(G * dk)
         us = timed(lambda: rk.qkv_prepare(
-            proj, q, H, G, dk, dv, kp, vp, table, ctx, bias=f(C), taps=f(C, taps),
-            kept=(state, 0), norm=("head", f(dk), f(dk), 1e-5),
+            proj, q, H, G, dk, dv, kp, vp, table, ctx, bias=qb, taps=qt,
+            kept=(state, 0), norm=("head", nq, nk, 1e-5),
             rotation=(freq, magnitude, True), mix=("take", v_first, lam)))
         record("qkv_prepare (biases, 3 taps, norms per head, rotation, mixed values)", case, us,
                bytes_=n * (C * 2 * (taps if n > s else 1) + H * dk * 2 + G * (dk + dv) * 2
                            + G * dv * 4) + (s * (taps - 1) * C * 4 if n == s else 0),
                like="kv_write_rotated")
         us = timed(lambda: rk.qkv_prepare(
-            proj, q, H, G, dk, dv, kp, vp, table, ctx, norm=("whole", f(H * dk), f(G * dk), 1e-5),
+            proj, q, H, G, dk, dv, kp, vp, table, ctx, norm=("whole", wq, wk, 1e-5),
             temperature=(0.5, 128), mix=("give", v_first)))
         record("qkv_prepare (norms over the projection, growing query)", case, us,
                bytes_=n * (C * 2 + H * dk * 2 + G * (dk + dv) * 2 + G * dv * 4),
@@ -1389,8 +1391,8 @@ def bizetar_kernels(peak: dict) -> list[dict]:
             record("experts gate and up (tensor cores)", case, us,
                    bytes_=2 * weights_read + pairs * (width + 2 * eff) * 2,
                    tensor_flops=4 * pairs * width * eff, like="experts up")
-            us = timed(lambda: ops.act_mul(both, inner, "silu"))
-            record("act_mul (silu(gate) * up of the slots)", case, us,
+            us = timed(lambda: ops.silu_mul(both, inner))
+            record("silu_mul (silu(gate) * up of the slots)", case, us,
                    bytes_=tiles * seg * eff * 6, like="silu_mul")
             us = timed(lambda: lk.experts_product(inner, down, pair_of, tile_expert, ye, True, None,
                                                   ctx.status))

@@ -256,7 +256,25 @@ struct Prepare {
     float* v_first;
 };
 
-template <typename T>
+// 16 bytes of the projection as floats
+__device__ __forceinline__ void load_piece(const float* p, float* f) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+}
+__device__ __forceinline__ void load_piece(const __nv_bfloat16* p, float* f) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        f[2 * i] = __uint_as_float(w[i] << 16);
+        f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+}
+
+// VEC: the rows of proj are whole 16-byte pieces at 16-byte addresses and C is a whole number of
+// pieces; a thread then takes the convolution of a piece's channels at once.  The sums are the
+// same chains of multiply-adds either way.
+template <typename T, bool VEC>
 __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __restrict__ q_out,
                                    const int* __restrict__ positions,
                                    const int* __restrict__ token_seq,
@@ -284,7 +302,35 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __rest
     }
     pdl_wait();
     const T* row = proj + (size_t)n * ld;
-    if (pp.taps != nullptr && pp.K > 1) {
+    if (VEC && pp.taps != nullptr && pp.K > 1) {
+        constexpr int PN = 16 / (int)sizeof(T);
+        const int K = pp.K;
+        const float* kept = pp.state + (size_t)slot * pp.slot_stride + pp.conv_offset;
+        for (int c0 = threadIdx.x * PN; c0 < C; c0 += blockDim.x * PN) {
+            float acc[PN], b[PN];
+#pragma unroll
+            for (int e = 0; e < PN; ++e) {
+                acc[e] = 0.0f;
+                b[e] = pp.bias ? pp.bias[c0 + e] : 0.0f;
+            }
+            for (int j = 0; j < K; ++j) {
+                const int rel = off - (K - 1) + j;
+                if (pos - (K - 1) + j < 0) continue;             // before the sequence's start
+                float x[PN];
+                if (rel >= 0) {
+                    load_piece(proj + (size_t)(n - (K - 1) + j) * ld + c0, x);
+                } else {
+#pragma unroll
+                    for (int e = 0; e < PN; ++e) x[e] = kept[(size_t)(off + j) * C + c0 + e];
+                }
+#pragma unroll
+                for (int e = 0; e < PN; ++e)
+                    acc[e] = fmaf(pp.taps[(c0 + e) * K + j], x[e] + b[e], acc[e]);
+            }
+#pragma unroll
+            for (int e = 0; e < PN; ++e) sh[c0 + e] = acc[e];
+        }
+    } else if (pp.taps != nullptr && pp.K > 1) {
         const int K = pp.K;
         const float* kept = pp.state + (size_t)slot * pp.slot_stride + pp.conv_offset;
         for (int c = threadIdx.x; c < C; c += blockDim.x) {
@@ -1550,22 +1596,28 @@ DE_EXPORT int de_qkv_prepare(int dtype, const void* proj, int ld, void* q_out,
     const int C = (H + G) * dk + G * dv;
     const size_t smem = (size_t)(C + rot + H + G) * sizeof(float);
     if (smem > 200 * 1024) return -2;
-    const int threads = n >= 512 ? 128 : (C >= 2048 ? 512 : 256);
-#define PREP(T)                                                                                 \
+    const int threads = C >= 2048 && n < 512 ? 512 : 256;
+    const int pn = dtype == DE_BF16 ? 8 : 4;
+    const bool vec = C % pn == 0 && ld % pn == 0 && (uintptr_t)proj % 16 == 0;
+#define PREP(T, V)                                                                              \
     do {                                                                                        \
         if (smem > 48 * 1024) {                                                                 \
-            cudaError_t e = cudaFuncSetAttribute(qkv_prepare_kernel<T>,                         \
+            cudaError_t e = cudaFuncSetAttribute(qkv_prepare_kernel<T, V>,                      \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize,   \
                                                  (int)smem);                                    \
             if (e != cudaSuccess) return (int)e;                                                \
         }                                                                                       \
-        return de_launch(qkv_prepare_kernel<T>, dim3(n), dim3(threads), smem, s, (const T*)proj, \
-                         ld, (T*)q_out, positions, token_seq, token_slot, seq_pos0, pp, H, G,   \
-                         dk, dv, (T*)k_pages, (T*)v_pages, block_table, table_stride, page,     \
-                         num_pages, status);                                                    \
+        return de_launch(qkv_prepare_kernel<T, V>, dim3(n), dim3(threads), smem, s,             \
+                         (const T*)proj, ld, (T*)q_out, positions, token_seq, token_slot,       \
+                         seq_pos0, pp, H, G, dk, dv, (T*)k_pages, (T*)v_pages, block_table,     \
+                         table_stride, page, num_pages, status);                                \
     } while (0)
-    if (dtype == DE_BF16) PREP(__nv_bfloat16);
-    PREP(float);
+    if (dtype == DE_BF16) {
+        if (vec) PREP(__nv_bfloat16, true);
+        PREP(__nv_bfloat16, false);
+    }
+    if (vec) PREP(float, true);
+    PREP(float, false);
 #undef PREP
 }
 

@@ -84,29 +84,119 @@ __global__ void depth_mix_kernel(const float* __restrict__ history, size_t strid
     }
 }
 
-template <typename T>
+// 16 bytes of T as floats and back
+template <typename T> struct Chunk;
+template <> struct Chunk<float> {
+    static constexpr int N = 4;
+    static __device__ __forceinline__ void load(const float* p, float* f) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        f[0] = v.x; f[1] = v.y; f[2] = v.z; f[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(float* p, const float* f) {
+        *reinterpret_cast<float4*>(p) = make_float4(f[0], f[1], f[2], f[3]);
+    }
+};
+template <> struct Chunk<__nv_bfloat16> {
+    static constexpr int N = 8;
+    static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* f) {
+        const uint4 u = *reinterpret_cast<const uint4*>(p);
+        const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            f[2 * i] = __uint_as_float(w[i] << 16);
+            f[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* f) {
+        unsigned w[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const __nv_bfloat162 h = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+            w[i] = *reinterpret_cast<const unsigned*>(&h);
+        }
+        *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+};
+
+// Three sums over a block at once; every thread gets the results.  The order of the additions
+// depends on the block's size only.
+__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float* scratch /* 99 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    c = warp_sum(c);
+    if (lane == 0) {
+        scratch[warp] = a;
+        scratch[32 + warp] = b;
+        scratch[64 + warp] = c;
+    }
+    __syncthreads();
+    if (warp < 3) {
+        float t = lane < warps ? scratch[32 * warp + lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[96 + warp] = t;
+    }
+    __syncthreads();
+    a = scratch[96];
+    b = scratch[97];
+    c = scratch[98];
+}
+
+// VEC: rows are whole 16-byte pieces at 16-byte addresses; a thread then takes pieces, and the
+// second pass finds the row in the caches.
+template <typename T, bool VEC>
 __global__ void poly_norm_kernel(const T* __restrict__ z, int ldz, const float* __restrict__ coef,
                                  T* __restrict__ out, int ldo, int cols, float eps) {
-    __shared__ float scratch[33];
+    __shared__ float scratch[99];
+    constexpr int PN = Chunk<T>::N;
     const size_t row = blockIdx.x;
     const T* zr = z + row * ldz;
     pdl_wait();
     float s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        const float v = to_float(zr[i]), v2 = v * v, v3 = v2 * v;
-        s1 = fmaf(v, v, s1);
-        s2 = fmaf(v2, v2, s2);
-        s3 = fmaf(v3, v3, s3);
+    if (VEC) {
+        for (int i = threadIdx.x * PN; i < cols; i += blockDim.x * PN) {
+            float f[PN];
+            Chunk<T>::load(zr + i, f);
+#pragma unroll
+            for (int e = 0; e < PN; ++e) {
+                const float v = f[e], v2 = v * v, v3 = v2 * v;
+                s1 = fmaf(v, v, s1);
+                s2 = fmaf(v2, v2, s2);
+                s3 = fmaf(v3, v3, s3);
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float v = to_float(zr[i]), v2 = v * v, v3 = v2 * v;
+            s1 = fmaf(v, v, s1);
+            s2 = fmaf(v2, v2, s2);
+            s3 = fmaf(v3, v3, s3);
+        }
     }
+    block_sum3(s1, s2, s3, scratch);
     const float n = (float)cols;
-    const float i1 = coef[0] / sqrtf(block_sum(s1, scratch) / n + eps);
-    const float i2 = coef[1] / sqrtf(block_sum(s2, scratch) / n + eps);
-    const float i3 = coef[2] / sqrtf(block_sum(s3, scratch) / n + eps);
-    const float e = coef[3];
+    const float i1 = coef[0] / sqrtf(s1 / n + eps);
+    const float i2 = coef[1] / sqrtf(s2 / n + eps);
+    const float i3 = coef[2] / sqrtf(s3 / n + eps);
+    const float e0 = coef[3];
     pdl_trigger();
-    for (int i = threadIdx.x; i < cols; i += blockDim.x) {
-        const float v = to_float(zr[i]), v2 = v * v;
-        out[row * ldo + i] = from_float<T>(v * i1 + v2 * i2 + v2 * v * i3 + e);
+    if (VEC) {
+        for (int i = threadIdx.x * PN; i < cols; i += blockDim.x * PN) {
+            float f[PN];
+            Chunk<T>::load(zr + i, f);
+#pragma unroll
+            for (int e = 0; e < PN; ++e) {
+                const float v = f[e], v2 = v * v;
+                f[e] = v * i1 + v2 * i2 + v2 * v * i3 + e0;
+            }
+            Chunk<T>::store(out + row * ldo + i, f);
+        }
+    } else {
+        for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+            const float v = to_float(zr[i]), v2 = v * v;
+            out[row * ldo + i] = from_float<T>(v * i1 + v2 * i2 + v2 * v * i3 + e0);
+        }
     }
 }
 
@@ -185,9 +275,17 @@ DE_EXPORT int de_poly_norm(int dtype, const void* z, int ldz, const float* coef,
     if (n <= 0 || cols <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = row_threads(cols);
-    if (dtype == DE_BF16)
-        return de_launch(poly_norm_kernel<__nv_bfloat16>, dim3(n), dim3(threads), 0, s,
-                         (const __nv_bfloat16*)z, ldz, coef, (__nv_bfloat16*)out, ldo, cols, eps);
-    return de_launch(poly_norm_kernel<float>, dim3(n), dim3(threads), 0, s, (const float*)z, ldz,
-                     coef, (float*)out, ldo, cols, eps);
+    const int pn = dtype == DE_BF16 ? 8 : 4;
+    const bool vec = cols % pn == 0 && ldz % pn == 0 && ldo % pn == 0 &&
+                     (uintptr_t)z % 16 == 0 && (uintptr_t)out % 16 == 0;
+#define POLY(T, V)                                                                             \
+    return de_launch(poly_norm_kernel<T, V>, dim3(n), dim3(threads), 0, s, (const T*)z, ldz,   \
+                     coef, (T*)out, ldo, cols, eps)
+    if (dtype == DE_BF16) {
+        if (vec) POLY(__nv_bfloat16, true);
+        POLY(__nv_bfloat16, false);
+    }
+    if (vec) POLY(float, true);
+    POLY(float, false);
+#undef POLY
 }

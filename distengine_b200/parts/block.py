@@ -106,14 +106,30 @@ class ResidualGate(Part):
     def __init__(self, width: int, dtype: torch.dtype, device: torch.device) -> None:
         super().__init__(dtype, device)
         self.width = width
-        self.weight = self.bias = None
+        self._host = self._weight = self.bias = None
 
     def tensors(self):
         return {"": ((self.width, self.width), "matrix"), ".b": ((self.width,), "bias")}
 
     def load(self, tensors):
-        self.weight = tensors[""].to(device=self.device, dtype=self.dtype).contiguous()
+        self._host = tensors[""]                 # until it is known who multiplies with it
+        self._weight = None
         self.bias = tensors[".b"].to(device=self.device, dtype=torch.float32).contiguous()
+
+    def host_matrix(self) -> torch.Tensor:
+        """The matrix on the host (stored dtype), for a sublayer that stacks it under its own
+        input matrix; afterwards call ``stacked()``."""
+        return self._host
+
+    def stacked(self) -> None:
+        self._host = None
+
+    @property
+    def weight(self) -> torch.Tensor:
+        if self._weight is None:
+            self._weight = self._host.to(device=self.device, dtype=self.dtype).contiguous()
+            self._host = None
+        return self._weight
 
     def kernel_modules(self):
         return ("sublayer",)
@@ -151,7 +167,12 @@ class SublayerNormBlock(Block):
 
     Gate, norm and sum are one kernel a sublayer, float32 throughout; it also leaves the new
     stream's rounding for the next products (``stream.rows``).  A layer without a feed-forward is
-    the first half only."""
+    the first half only.
+
+    A sublayer whose only use of its input is one product (it has ``input_matrix()`` and
+    ``run(proj, ...)``, as the projected mixers have) shares that product with its gate: the
+    gate's matrix is stacked under the sublayer's, so the input is read once and a sublayer
+    has one launch less."""
 
     def __init__(self, mixer, feed_forward, mixer_norm, feed_forward_norm, side_input=None,
                  gated: bool = False, depth: int = 0) -> None:
@@ -168,6 +189,7 @@ class SublayerNormBlock(Block):
         self.feed_forward_gate = (ResidualGate(width, dtype, device)
                                   if gated and feed_forward is not None else None)
         self.depth_mix = DepthMix(depth, dtype, device) if depth else None
+        self._stacks: dict = {}      # role -> (the sublayer's and the gate's matrices, gate column)
 
     def history_depth(self) -> int:
         return self.depth_mix.count if self.depth_mix is not None else 0
@@ -179,12 +201,34 @@ class SublayerNormBlock(Block):
                 parts[role] = getattr(self, role)
         return parts
 
-    def _join(self, y, gate, norm, h, stream, ctx, out, rows):
-        """out = stream + norm(y * gate(h)); ``rows``: where its rounding goes (or None)."""
+    def _sublayer(self, role, part, gate, h, ctx, cache=None):
+        """(the sublayer's result, the gate's product on the same input h)."""
         if gate is None:
             raise NotImplementedError("sublayer_norm: only the gated form has a kernel")
-        z = ctx.buffer("block.gate", (h.shape[0], gate.width))
+        n = h.shape[0]
+        if hasattr(part, "input_matrix") and hasattr(part, "run"):
+            stack = self._stacks.get(role)
+            if stack is None:
+                from .base import compute_matrix
+                from .recurrent import stack_segments
+                both, offsets = stack_segments([part.input_matrix(), gate.host_matrix()])
+                stack = self._stacks[role] = (compute_matrix(both, part.dtype, part.device),
+                                              offsets[1])
+                part.finish_load()
+                gate.stacked()
+            w_in, col = stack
+            proj = ctx.buffer(f"block.{role}.proj", (n, w_in.shape[0]))
+            ops.linear(h, w_in, out=proj, status=ctx.status)
+            y = part.run(proj, ctx, cache) if role == "mixer" else part.run(proj, ctx)
+            return y, proj[:, col: col + gate.width]
+        y = part.forward(h, ctx, cache) if role == "mixer" else part.forward(h, ctx)
+        z = ctx.buffer("block.gate", (n, gate.width))
         ops.linear(h, gate.weight, out=z, status=ctx.status)
+        return y, z
+
+    def _join(self, y, z, gate, norm, stream, ctx, out, rows):
+        """out = stream + norm(y * sigmoid(z + b)); ``rows``: where its rounding goes (or
+        None)."""
         ops.gated_normed_add(y, z, gate.bias, norm.weight, norm.eps, stream.resid, out, rows)
 
     def forward(self, stream: ResidualStream, ctx: StepContext, cache: "CacheBinding | None",
@@ -210,13 +254,14 @@ class SublayerNormBlock(Block):
                                    f"stream, {stream.history_count + 1} exist")
             result = stream.history[self.depth_mix.count - 1]
         last = self.feed_forward is None
-        y = self.mixer.forward(h, ctx, cache)
-        self._join(y, self.mixer_gate, self.mixer_norm, h, stream, ctx,
+        y, z = self._sublayer("mixer", self.mixer, self.mixer_gate, h, ctx, cache)
+        self._join(y, z, self.mixer_gate, self.mixer_norm, stream, ctx,
                    result if last else resid, None if (last and self.depth_mix) else rows)
         if not last:
             h = resid if wide else rows
-            y = self.feed_forward.forward(h, ctx)
-            self._join(y, self.feed_forward_gate, self.feed_forward_norm, h, stream, ctx, result,
+            y, z = self._sublayer("feed_forward", self.feed_forward, self.feed_forward_gate, h,
+                                  ctx)
+            self._join(y, z, self.feed_forward_gate, self.feed_forward_norm, stream, ctx, result,
                        None if self.depth_mix else rows)
         if self.depth_mix is not None:
             stream.history_count += 1

@@ -102,7 +102,9 @@ class RoutedExperts(FeedForward):
                                ctx.status)
         else:
             lk.experts_up(x, self.up, pair_of, tile_expert, top, first, first_act)
-        if self.gated:
+        if self.gated and self.activation == "silu":
+            ops.silu_mul(first, inner)                     # the vectorised form
+        elif self.gated:
             ops.act_mul(first, inner, self.activation)
         if tensor:
             lk.experts_product(inner, self.down, pair_of, tile_expert, y, True, None, ctx.status)

@@ -126,7 +126,8 @@ class PolyNormMLP(FeedForward):
 
     def load(self, tensors):
         up, down = self.names
-        self.w_up = compute_matrix(tensors[up], self.dtype, self.device)
+        self._host_up = tensors[up]
+        self.w_up = None
         self.w_down = compute_matrix(tensors[down], self.dtype, self.device)
         self.coef = tensors[self.coefficients].to(device=self.device,
                                                   dtype=torch.float32).contiguous()
@@ -134,10 +135,24 @@ class PolyNormMLP(FeedForward):
     def kernel_modules(self):
         return ("sublayer",)
 
+    # all this part takes from its input is the up product: whoever owns a wider product stacks
+    # ``input_matrix()`` into it and calls ``run`` on that product's rows (row stride free)
+    def input_matrix(self) -> torch.Tensor:
+        return self._host_up
+
+    def finish_load(self) -> None:
+        self._host_up = None
+
     def forward(self, x: torch.Tensor, ctx: StepContext, ahead=None) -> torch.Tensor:
-        n = x.shape[0]
-        z = ctx.buffer("mlp.up", (n, self.inner))
+        if self.w_up is None:
+            self.w_up = compute_matrix(self._host_up, self.dtype, self.device)
+            self.finish_load()
+        z = ctx.buffer("mlp.up", (x.shape[0], self.inner))
         ops.linear(x, self.w_up, out=z, status=ctx.status)
+        return self.run(z, ctx)
+
+    def run(self, proj: torch.Tensor, ctx: StepContext) -> torch.Tensor:
+        n, z = proj.shape[0], proj[:, : self.inner]
         act = ctx.buffer("mlp.act", (n, self.inner))
         ops.poly_norm(z, self.coef, self.eps, act)
         out = ctx.buffer("mlp.out", (n, self.width))
