@@ -103,7 +103,9 @@ def _mixer(kind: str, m: Mapping[str, Any], where: str) -> dict:
         out["conv"] = taps or 0
         out["rot"] = _rotation(m, where, out["dim"])
         allowed = {"conv", "rot"}
-    unknown = set(m) - allowed - {"heads", "kv_heads", "dim", "vdim", "scale", "v_mix"}
+    # a key of the other form may stand with null or false (nothing of it is there)
+    unknown = {k for k in set(m) - allowed - {"heads", "kv_heads", "dim", "vdim", "scale", "v_mix"}
+               if m[k] is not None and m[k] is not False}
     if unknown:
         raise ConfigError(f"config.json: '{where}' has keys this design does not know for "
                           f"'{kind}': {sorted(unknown)}")
@@ -163,10 +165,10 @@ class BizetarConfig(ModelConfig):
                                   f"{' and '.join(repr(k) for k in KINDS)}")
             mixer = _mixer(kind, _section(entry, "mixer", where), where + "mixer.")
             layers.append((kind, _freeze(mixer), _freeze(_feed_forward(entry.get("mlp"), where))))
-        sizes = {(dict(m)["kv_heads"], dict(m)["vdim"]) for _, m, _ in layers if dict(m)["v_mix"]}
+        sizes = {dict(m)["kv_heads"] * dict(m)["vdim"] for _, m, _ in layers if dict(m)["v_mix"]}
         if len(sizes) > 1:
             raise ConfigError("config.json: the layers with 'v_mix' must have values of one size "
-                              f"(kv_heads, vdim), got {sorted(sizes)}")
+                              f"(kv_heads * vdim numbers a token), got {sorted(sizes)}")
         return BizetarConfig(architecture=NAME,
                              vocab=positive("vocab", require(data, "vocab", int)),
                              model_width=width, eps=eps, layers=tuple(layers))
@@ -270,6 +272,18 @@ class BizetarConfig(ModelConfig):
 
     def final_norm(self) -> PartSpec:
         return self._norm("norm")
+
+    def unused_tensors(self) -> set[str]:
+        """Tensors that a weight file of this design may hold for parts that a layer does not
+        have: the mixing weight of a layer outside the mixing of values, and the second
+        sublayer's norm and gate of a layer without a feed-forward."""
+        names = set()
+        for i, (_, mixer, mlp) in enumerate(self.layers):
+            if not dict(mixer)["v_mix"]:
+                names.add(f"l{i}.mix.vmix")
+            if mlp is None:
+                names |= {f"l{i}.norm2", f"l{i}.rg2", f"l{i}.rg2.b"}
+        return names
 
     def tensor_names(self) -> dict[str, str]:
         return {"embedding": "embed", "embedding_norm": "embed.", "final_norm": "final.",

@@ -125,6 +125,11 @@ class ModelConfig:
         """role -> tensor name of the tensors outside the layers."""
         raise NotImplementedError
 
+    def unused_tensors(self) -> set[str]:
+        """Names that a weight file may hold although this model has no use for them; they are
+        passed over instead of being reported as unexpected."""
+        return set()
+
     def to_json(self) -> dict[str, Any]:
         """The config.json that parses back to this configuration."""
         raise NotImplementedError

@@ -18,6 +18,6 @@ def load_model(model_dir: str, dtype: "str | torch.dtype" = torch.bfloat16,
     architecture, config = read_config(model_dir)
     model = architecture.build_model(config, dtype, device)
     expected, _, optional = model.expected_tensors()
-    tensors = load_checked(model_dir, expected, optional, dtype)
+    tensors = load_checked(model_dir, expected, optional, dtype, unused=config.unused_tensors())
     model.load(tensors)
     return model

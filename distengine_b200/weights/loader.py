@@ -75,10 +75,12 @@ def _fits(shape, wanted) -> bool:
 
 def load_checked(model_dir: str, expected: dict[str, tuple[int, ...]],
                  optional: set[str] = frozenset(), dtype: torch.dtype = torch.bfloat16,
-                 integer: set[str] = frozenset()) -> dict[str, torch.Tensor]:
+                 integer: set[str] = frozenset(),
+                 unused: set[str] = frozenset()) -> dict[str, torch.Tensor]:
     """Every tensor of ``expected`` (name -> shape) from the folder's safetensors files.
 
-    ``optional`` names may be absent (a tied output matrix).  ``integer`` names are integer
+    ``optional`` names may be absent (a tied output matrix).  ``unused`` names may be present
+    although nothing reads them (``ModelConfig.unused_tensors``).  ``integer`` names are integer
     tables; every other tensor must be stored in a floating-point dtype.  Raises
     ``WeightMismatchError`` with all missing and unexpected names, wrong shapes and wrong dtypes
     at once.  Tensors come back on the host.
@@ -87,7 +89,7 @@ def load_checked(model_dir: str, expected: dict[str, tuple[int, ...]],
     error = WeightMismatchError(where=model_dir)
     for handle in open_model_files(model_dir):
         for name in handle.names():
-            if name.endswith(IGNORED_SUFFIXES):
+            if name.endswith(IGNORED_SUFFIXES) or (name in unused and name not in expected):
                 continue
             if name not in expected:
                 error.unexpected.append(name)

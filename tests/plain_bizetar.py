@@ -123,7 +123,7 @@ def mix_values(v, lam, v_first):
     if v_first is None:
         return v
     lam = lam.to(v.dtype)
-    return (1.0 - lam) * v + lam * v_first
+    return (1.0 - lam) * v + lam * v_first.reshape(v.shape)       # number by number
 
 
 # ----------------------------------------------------------------------------- mixers

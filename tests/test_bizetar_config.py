@@ -70,6 +70,38 @@ def test_what_a_layer_keeps():
     assert all(isinstance(s, PagedKVSpec) for s in one_tap)
 
 
+def test_null_keys_of_the_other_form_and_unused_tensors(tmp_path):
+    """A key of the other mixer form may stand with null; a weight file may hold the mixing
+    weight of a layer outside the mixing and the second sublayer's tensors of a layer without a
+    feed-forward - they are passed over, anything else unexpected is still reported."""
+    import torch
+    from distengine_b200.weights import save_tensors
+    from distengine_b200.weights.loader import WeightMismatchError, load_checked
+    config = copy.deepcopy(bc.BIZ_A)
+    config["layers"][0]["mixer"].update(conv=None, rot=None)
+    config["layers"][1]["mixer"].update(q_temp=None)
+    parsed = BizetarConfig.from_json(config)
+    assert parsed == BizetarConfig.from_json(bc.BIZ_A)
+    assert parsed.unused_tensors() == {"l2.mix.vmix", "l2.norm2", "l2.rg2", "l2.rg2.b"}
+    expected, _, optional = expected_tensors(parsed)
+    tensors = {k: torch.zeros(v) for k, v in expected.items()}
+    tensors.update({"l2.mix.vmix": torch.zeros(()), "l2.norm2": torch.zeros(42),
+                    "l2.rg2": torch.zeros(42, 42), "l2.rg2.b": torch.zeros(42)})
+    save_tensors(str(tmp_path / "model.safetensors"), tensors)
+    loaded = load_checked(str(tmp_path), expected, optional, torch.float32,
+                          unused=parsed.unused_tensors())
+    assert set(loaded) == set(expected)
+    with pytest.raises(WeightMismatchError) as error:
+        load_checked(str(tmp_path), expected, optional, torch.float32)
+    assert "l2.rg2.b" in str(error.value)
+    tensors["l0.mix.q.b"] = torch.zeros(30)
+    save_tensors(str(tmp_path / "model.safetensors"), tensors)
+    with pytest.raises(WeightMismatchError) as error:
+        load_checked(str(tmp_path), expected, optional, torch.float32,
+                     unused=parsed.unused_tensors())
+    assert "l0.mix.q.b" in str(error.value) and "l2.rg2" not in str(error.value)
+
+
 def _broken(change):
     config = copy.deepcopy(bc.BIZ_A)
     change(config)
@@ -90,6 +122,7 @@ def _broken(change):
     (lambda c: c["layers"][0]["mlp"].update(kind="sparse"), "layers[0].mlp.kind"),
     (lambda c: c["layers"][1]["mixer"]["rot"]["scaling"].update(factor=0), "rot.scaling"),
     (lambda c: c["layers"][3]["mixer"].update(vdim=4), "v_mix"),
+    (lambda c: c["layers"][0]["mixer"].update(rot={"base": 10.0, "dims": 2}), "layers[0].mixer."),
     (lambda c: c["norm"].update(eps=0), "norm.eps"),
 ])
 def test_errors_name_the_key(change, key):

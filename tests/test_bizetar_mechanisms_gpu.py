@@ -135,15 +135,16 @@ def test_sink_attention_in_portions(dtype, entry, page):
 
 
 def test_values_are_mixed_between_layers():
-    """Three mixers in one step: the first gives its values, the second takes them with its own
-    lambda, the third stays out; what the second caches is the mixed value (decoded tokens read
-    it back)."""
+    """Four mixers in one step: the first gives its values, the second takes them with its own
+    lambda, the third stays out, the fourth takes them with as many numbers a token in another
+    split into heads; what a taker caches is the mixed value (decoded tokens read it back)."""
     config = _model(40, [
         bc.layer("attention", bc.first(4, 2, 8, 6, 0.3), None),
         bc.layer("attention_2", bc.second(6, 2, 4, 6, 0.4, conv=3, rot=(100.0, 4)), None),
-        bc.layer("attention_2", bc.second(2, 1, 8, 5, 0.4, v_mix=False, conv=2), None)])
+        bc.layer("attention_2", bc.second(2, 1, 8, 5, 0.4, v_mix=False, conv=2), None),
+        bc.layer("attention_2", bc.second(3, 1, 8, 12, 0.4), None)])
     mixers, _, wd = _build(config, torch.float32)
-    assert [m.value_mix for m in mixers] == ["give", "take", None]
+    assert [m.value_mix for m in mixers] == ["give", "take", None, "take"]
     g = _gen(8)
     xs = {"a": torch.randn(60, 40, generator=g), "b": torch.randn(33, 40, generator=g)}
     h = PartHarness(mixers, [m.cache_spec() for m in mixers], torch.float32, page_size=8,
@@ -152,7 +153,7 @@ def test_values_are_mixed_between_layers():
     got = _run_in_portions(mixers, h, xs, portions)
     for rid, x in xs.items():
         want = _plain_mixers(config, wd, x.double())
-        for index in range(3):
+        for index in range(4):
             assert_close(got[index][rid], want[index], torch.float32, f"mixer {index} {rid}")
     # without the mixing the second mixer gives something else
     plain = dict(config["layers"][1]["mixer"], v_mix=False)
