@@ -1146,12 +1146,12 @@ def bizetar_shape(layers: int) -> dict:
     feed-forward of the headline's size in every fourth layer and 16 gated experts of 1,024 inner
     features beside 4 outputs that hand the input on, 4 a token, in the others (about as many
     active feed-forward weights as the dense layers have).  Every layer mixes values."""
-    rot = {"dims": 128, "base": 50000.0,
-           "scaling": {"factor": 8.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    rot = {"dims": 128, "base": 100000.0,
+           "scaling": {"factor": 16.0, "original": 4096, "fast": 16.0, "slow": 2.0}}
     common = {"heads": 16, "kv_heads": 4, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
               "v_mix": True}
     second = {"type": "attention_2", "mixer": dict(common, conv=3, rot=rot)}
-    first = {"type": "attention", "mixer": dict(common, q_temp={"coef": 0.5, "every": 128})}
+    first = {"type": "attention", "mixer": dict(common, q_temp={"coef": 0.3, "every": 256})}
     dense = {"kind": "dense", "ff": MODEL["intermediate_size"]}
     routed = {"kind": "moe", "expert": {"ff": 1024},
               "router": {"experts": 16, "top": 4, "identity": 4}}
@@ -1302,7 +1302,7 @@ def bizetar_kernels(peak: dict) -> list[dict]:
                like="kv_write_rotated")
         us = timed(lambda: rk.qkv_prepare(
             proj, q, H, G, dk, dv, kp, vp, table, ctx, norm=("whole", wq, wk, 1e-5),
-            temperature=(0.5, 128), mix=("give", v_first)))
+            temperature=(0.3, 256), mix=("give", v_first)))
         record("qkv_prepare (norms over the projection, growing query)", case, us,
                bytes_=n * (C * 2 + H * dk * 2 + G * (dk + dv) * 2 + G * dv * 4),
                like="kv_write_rotated")

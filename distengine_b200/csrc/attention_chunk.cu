@@ -23,6 +23,15 @@
 // A block then walks the tiles of the kept first keys and jumps to the tile in which its rows'
 // windows begin.  r1 / r2 null: no distance penalty.  `out_f32`: the rows' results are written as
 // float32 (for a kernel that turns them by position or gates them before they are rounded).
+//
+// Three more parameters of `Sight` serve attention whose softmax has a sink: a distance penalty
+// that is linear, r1[h] * (i - j); `sink` [heads], a learned score per head that joins the
+// denominator as exp(sink[h]) without a key or a value (it is added once, when a row's sums are
+// complete, whatever the tiles and the step's cut); and `gate`, sigmoid of which multiplies a
+// row's result in float32 before it is stored (one number a feature or one a head).  qkv_prepare
+// is what stands between such a mixer's projection and these kernels (bias, a short convolution
+// over time with the slot's kept rows, norms, rotation, value mixing, the cache write), and
+// conv_keep moves the kept rows on.
 
 #include "common.cuh"
 

@@ -66,7 +66,7 @@ BIZ_A = {
 BIZ_B = {
     "architecture": "Bizetar", "vocab": 97, "width": 64, "norm": {"eps": 1e-6},
     "layers": [
-        layer("attention_2", second(20, 2, 16, 8, 0.2, rot=(50000.0, 8, (8.0, 32, 16.0, 1.0))),
+        layer("attention_2", second(20, 2, 16, 8, 0.2, rot=(70000.0, 8, (8.0, 32, 16.0, 1.0))),
               moe(4, 6, 16, identity=2)),
         layer("attention", first(8, 4, 16, 8, 0.25, v_mix=False, q_temp=(0.3, 1)), dense(96)),
         layer("attention_2", second(4, 2, 32, 8, 0.15, conv=1, rot=(1000.0, 32)),
@@ -92,10 +92,10 @@ BIZ_C = {
 BIZ_WIDE = {
     "architecture": "Bizetar", "vocab": 300, "width": 256, "norm": {"eps": 1e-6},
     "layers": [
-        layer("attention_2", second(12, 2, 64, 32, 0.12, conv=3,
-                                    rot=(50000.0, 64, (8.0, 256, 32.0, 1.0))),
-              moe(8, 3, 128, identity=4)),
-        layer("attention", first(8, 2, 48, 32, 0.14, q_temp=(0.5, 128)), dense(512)),
+        layer("attention_2", second(12, 2, 64, 40, 0.12, conv=2,
+                                    rot=(40000.0, 48, (6.0, 256, 16.0, 2.0))),
+              moe(6, 2, 128, identity=3)),
+        layer("attention", first(8, 2, 56, 40, 0.14, q_temp=(0.4, 96)), dense(512)),
     ],
 }
 

@@ -105,7 +105,7 @@ MIXERS = [
     # whole pieces, up to 8 heads a kv head: single tokens take the one-block kernel
     (bc.layer("attention", bc.first(8, 1, 16, 8, 0.25, q_temp=(0.3, 1)), None), 8),
     (bc.layer("attention_2", bc.second(8, 2, 16, 16, 0.25, conv=3,
-                                       rot=(50000.0, 16, (8.0, 32, 16.0, 1.0))), None), 8),
+                                       rot=(30000.0, 16, (8.0, 32, 16.0, 1.0))), None), 8),
     # more than 8 heads a kv head; no convolution, rotation of a part without stretch
     (bc.layer("attention_2", bc.second(12, 1, 8, 8, 0.3, rot=(1000000.0, 4)), None), 16),
     # one head, values of size 1, five taps, nothing rotated
@@ -172,7 +172,7 @@ def test_one_key_among_hundreds_decides(kind, far, decoded):
     the result."""
     width, T, dk = 40, 420, 32
     if kind == "attention":
-        entry = bc.layer(kind, bc.first(4, 1, dk, 12, 1.0, q_temp=(0.5, 128)), None)
+        entry = bc.layer(kind, bc.first(4, 1, dk, 12, 1.0, q_temp=(0.4, 96)), None)
     else:
         entry = bc.layer(kind, bc.second(4, 1, dk, 12, 1.0,
                                          rot=(10000.0, 4, (8.0, 64, 32.0, 1.0))), None)
@@ -394,7 +394,7 @@ def test_stretched_frequencies_and_adjacent_pairs():
     """The engine's frequency table against the plain one, and the turn of adjacent pairs with the
     grown cosine and sine against a rotation written with complex numbers."""
     from distengine_b200.parts.sink_attention import stretched_frequencies
-    for base, dims, stretch in ((50000.0, 64, (8.0, 2048, 32.0, 1.0)), (100.0, 6, (4.0, 16, 8.0, 1.0)),
+    for base, dims, stretch in ((40000.0, 48, (6.0, 1024, 16.0, 2.0)), (100.0, 6, (4.0, 16, 8.0, 1.0)),
                                 (10000.0, 8, None), (20.0, 2, (40.0, 100, 2.0, 0.5))):
         scaling = None if stretch is None else dict(zip(("factor", "original", "fast", "slow"),
                                                         stretch))
