@@ -280,6 +280,35 @@ __device__ __forceinline__ void load_piece(const __nv_bfloat16* p, float* f) {
     }
 }
 
+// two neighbouring features in one store
+__device__ __forceinline__ void store_pair(float* p, float a, float b) {
+    *reinterpret_cast<float2*>(p) = make_float2(a, b);
+}
+__device__ __forceinline__ void store_pair(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+// Two sums over a block at once; every thread gets both.  The order of the additions depends on
+// the block's size only.
+__device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch /* 66 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int warps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a);
+    b = warp_sum(b);
+    if (lane == 0) {
+        scratch[warp] = a;
+        scratch[32 + warp] = b;
+    }
+    __syncthreads();
+    if (warp < 2) {
+        float t = lane < warps ? scratch[32 * warp + lane] : 0.0f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[64 + warp] = t;
+    }
+    __syncthreads();
+    a = scratch[64];
+    b = scratch[65];
+}
+
 // VEC: the rows of proj are whole 16-byte pieces at 16-byte addresses and C is a whole number of
 // pieces; a thread then takes the convolution of a piece's channels at once.  The sums are the
 // same chains of multiply-adds either way.
@@ -293,7 +322,7 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __rest
                                    const int* __restrict__ block_table, int table_stride, int page,
                                    int num_pages, int* __restrict__ status) {
     extern __shared__ float sh[];
-    __shared__ float scratch[33];
+    __shared__ float scratch[66];
     const int n = blockIdx.x;
     const int qk = (H + G) * dk, C = qk + G * dv, half = pp.rot / 2;
     float* cs_tab = sh + C;                          // [half] cosines, then [half] sines
@@ -354,6 +383,17 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __rest
             }
             sh[c] = acc;
         }
+    } else if (VEC) {
+        constexpr int PN = 16 / (int)sizeof(T);
+        for (int c0 = threadIdx.x * PN; c0 < C; c0 += blockDim.x * PN) {
+            float x[PN];
+            load_piece(row + c0, x);
+#pragma unroll
+            for (int e = 0; e < PN; ++e) {
+                x[e] += pp.bias ? pp.bias[c0 + e] : 0.0f;
+                sh[c0 + e] = pp.taps != nullptr ? pp.taps[c0 + e] * x[e] : x[e];   // one tap
+            }
+        }
     } else {
         const float tap = pp.taps != nullptr ? 1.0f : 0.0f;     // a convolution of one tap
         for (int c = threadIdx.x; c < C; c += blockDim.x) {
@@ -374,8 +414,9 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __rest
         float sq = 0.0f, sk = 0.0f;
         for (int i = threadIdx.x; i < H * dk; i += blockDim.x) sq = fmaf(sh[i], sh[i], sq);
         for (int i = H * dk + threadIdx.x; i < qk; i += blockDim.x) sk = fmaf(sh[i], sh[i], sk);
-        const float iq = 1.0f / sqrtf(block_sum(sq, scratch) / (float)(H * dk) + pp.eps);
-        const float ik = 1.0f / sqrtf(block_sum(sk, scratch) / (float)(G * dk) + pp.eps);
+        block_sum2(sq, sk, scratch);
+        const float iq = 1.0f / sqrtf(sq / (float)(H * dk) + pp.eps);
+        const float ik = 1.0f / sqrtf(sk / (float)(G * dk) + pp.eps);
         for (int h = threadIdx.x; h < H + G; h += blockDim.x) inv_s[h] = h < H ? iq : ik;
     }
     __syncthreads();
@@ -383,8 +424,30 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __rest
     float temp = 1.0f;
     if (pp.temp_every > 0) temp = 1.0f + pp.temp_coef * logf((float)((pos + 1) / pp.temp_every) + 1.0f);
     const size_t at = ((size_t)(can_write ? page_id : 0) * G) * page + (size_t)(pos % page);
+    const bool paired = dk % 2 == 0 && (pp.adjacent || half == 0);
+    // neighbouring features two at a time (turned together, or both plain), one store for both
+    for (int idx = threadIdx.x; idx < (paired ? (H + G) * (dk / 2) : 0); idx += blockDim.x) {
+        const int h = idx / (dk / 2), i = idx - h * (dk / 2);
+        const bool is_q = h < H;
+        if (!is_q && !can_write) continue;
+        const float* x = sh + h * dk;
+        const float* wt = nullptr;
+        float inv = 1.0f;
+        if (pp.norm != 0) {
+            inv = inv_s[h];
+            wt = is_q ? pp.q_weight : pp.k_weight;
+            if (pp.norm == 2) wt += (is_q ? h : h - H) * dk;
+        }
+        const float mul = is_q ? temp : 1.0f;
+        T* dst = is_q ? q_out + (size_t)n * (H * dk) + h * dk
+                      : k_pages + (at + (size_t)(h - H) * page) * dk;
+        const int a = 2 * i, b = a + 1;
+        float ra = x[a] * inv * (wt ? wt[a] : 1.0f), rb = x[b] * inv * (wt ? wt[b] : 1.0f);
+        if (i < half) rope_rotate(ra, rb, cs_tab[i], cs_tab[half + i], ra, rb);
+        store_pair(dst + a, ra * mul, rb * mul);
+    }
     const int per = dk - half;                       // work items a head: pairs, then plain features
-    for (int idx = threadIdx.x; idx < (H + G) * per; idx += blockDim.x) {
+    for (int idx = threadIdx.x; idx < (paired ? 0 : (H + G) * per); idx += blockDim.x) {
         const int h = idx / per, i = idx - h * per;
         const bool is_q = h < H;
         if (!is_q && !can_write) continue;
