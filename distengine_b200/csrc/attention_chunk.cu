@@ -231,7 +231,9 @@ __global__ void kv_write_rotated_kernel(T* __restrict__ proj, int ld, const int*
 //   taps      a short causal convolution over time on every channel, y_t = sum_j taps[c][j] *
 //             u_(t - K + 1 + j), zeros before the sequence's start; inputs before the step's first
 //             token of the sequence come from the slot's state, kept[i] = projection (without
-//             bias) at position pos0 - (K - 1) + i, as conv_keep leaves them
+//             bias) at position pos0 - (K - 1) + i, as conv_keep leaves them; with keep_here (a
+//             step in which every sequence brings one token, so no other block reads the
+//             slot) the block moves the kept rows on itself and conv_keep is not needed
 //   norm      q and k divided by their root mean square (eps inside the root) and weighted: 1 over
 //             every head with weights [dk] that all heads share, 2 over the whole projection with
 //             weights [H dk] and [G dk]
@@ -247,7 +249,7 @@ struct Prepare {
     const float* bias;
     const float* taps;
     int K;
-    const float* state;
+    float* state;
     long long slot_stride;
     int conv_offset;
     int norm;
@@ -263,6 +265,7 @@ struct Prepare {
     int mix;
     const float* lambda;
     float* v_first;
+    int keep_here;
 };
 
 // 16 bytes of the projection as floats
@@ -402,6 +405,14 @@ __global__ void qkv_prepare_kernel(const T* __restrict__ proj, int ld, T* __rest
         }
     }
     __syncthreads();
+    if (pp.keep_here && pp.taps != nullptr && pp.K > 1) {
+        // every thread has read what it needs of the kept rows; a thread moves its channels on
+        float* kept = pp.state + (size_t)slot * pp.slot_stride + pp.conv_offset;
+        for (int c = threadIdx.x; c < C; c += blockDim.x) {
+            for (int i = 0; i + 2 < pp.K; ++i) kept[(size_t)i * C + c] = kept[(size_t)(i + 1) * C + c];
+            kept[(size_t)(pp.K - 2) * C + c] = to_float(row[c]);
+        }
+    }
     if (pp.norm == 1) {
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
         for (int h = warp; h < H + G; h += warps) {
@@ -1648,13 +1659,14 @@ DE_EXPORT int de_kv_write_rotated(int dtype, void* proj, int ld, const int* posi
 DE_EXPORT int de_qkv_prepare(int dtype, const void* proj, int ld, void* q_out,
                              const int* positions, const int* token_seq, const int* token_slot,
                              const int* seq_pos0, const float* bias, const float* taps, int K,
-                             const float* state, long long slot_stride, int conv_offset, int norm,
+                             float* state, long long slot_stride, int conv_offset, int norm,
                              const float* q_weight, const float* k_weight, float eps,
                              const float* freq, int rot, float magnitude, int adjacent,
                              float temp_coef, int temp_every, int mix, const float* lambda,
-                             float* v_first, int H, int G, int dk, int dv, void* k_pages,
-                             void* v_pages, const int* block_table, int table_stride, int page,
-                             int num_pages, int n, int* status, void* stream) {
+                             float* v_first, int keep_here, int H, int G, int dk, int dv,
+                             void* k_pages, void* v_pages, const int* block_table,
+                             int table_stride, int page, int num_pages, int n, int* status,
+                             void* stream) {
     if (n <= 0) return 0;
     if (rot < 0 || rot % 2 || rot > dk || (rot > 0 && freq == nullptr) || norm < 0 || norm > 2 ||
         (norm != 0 && (q_weight == nullptr || k_weight == nullptr)) || mix < 0 || mix > 2 ||
@@ -1663,7 +1675,7 @@ DE_EXPORT int de_qkv_prepare(int dtype, const void* proj, int ld, void* q_out,
         return -2;
     const Prepare pp = {bias, taps, K, state, slot_stride, conv_offset, norm, q_weight, k_weight,
                         eps, freq, rot, magnitude, adjacent, temp_coef, temp_every, mix, lambda,
-                        v_first};
+                        v_first, keep_here};
     cudaStream_t s = (cudaStream_t)stream;
     const int C = (H + G) * dk + G * dv;
     const size_t smem = (size_t)(C + rot + H + G) * sizeof(float);

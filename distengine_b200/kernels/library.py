@@ -81,7 +81,7 @@ SIGNATURES: dict[str, dict[str, list]] = {
         "de_attn_finish": [I, P, P, P, P, I, P, I, I, I, I, P],
         "de_conv_keep": [I, P, I, P, L, I, P, P, P, I, I, I, P],
         "de_qkv_prepare": [I, P, I, P, P, P, P, P, P, P, I, P, L, I, I, P, P, F, P, I, F, I, F, I,
-                           I, P, P, I, I, I, I, P, P, P, I, I, I, I, P, P],
+                           I, P, P, I, I, I, I, I, P, P, P, I, I, I, I, P, P],
         "de_kv_write_normed": [I, P, I, I, P, P, I, I, I, F, P, P, P, I, I, I, I, P, P],
         "de_attn_chunk": [I, P, I, P, I, P, P, P, I, I, P, P, P, P, P, I, P, P, I, I, I, I, I, F,
                           I, I, I, F, I, I, I, I, P, P, I, I, P, P],

@@ -495,7 +495,8 @@ def qkv_prepare(proj: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: i
                 block_table: torch.Tensor, ctx, bias: "torch.Tensor | None" = None,
                 taps: "torch.Tensor | None" = None, kept: "tuple | None" = None,
                 norm: "tuple | None" = None, rotation: "tuple | None" = None,
-                temperature: "tuple | None" = None, mix: "tuple | None" = None) -> None:
+                temperature: "tuple | None" = None, mix: "tuple | None" = None,
+                keep_here: bool = False) -> None:
     """From the stacked projection ``proj`` = [q (H dk) | k (G dk) | v (G dv) | ...] to the
     queries ``q_out`` [N, H dk] and the keys and values in the pages, through (each optional, in
     this order): ``bias`` float32 [C] (C = (H + G) dk + G dv); ``taps`` float32 [C, K], a causal
@@ -503,7 +504,9 @@ def qkv_prepare(proj: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: i
     offset), laid out as ``conv_keep`` leaves them; ``norm`` = (mode, q weight, k weight, eps),
     mode "head" (weights [dk]) or "whole" (weights [H dk], [G dk]); ``rotation`` = (freq
     [rot / 2], magnitude, adjacent); ``temperature`` = (coef, every) on q; ``mix`` = ("give",
-    v_first) or ("take", v_first, lambda [1]) with v_first float32 [N, G dv]."""
+    v_first) or ("take", v_first, lambda [1]) with v_first float32 [N, G dv].  ``keep_here``:
+    only for a step in which every sequence brings one token - the kernel then also moves the
+    slots' kept rows on, and no ``conv_keep`` follows."""
     n = proj.shape[0]
     channels = (heads + kv_heads) * key_dim + kv_heads * value_dim
     _need(proj.stride(1) == 1 and proj.shape[1] >= channels and proj.dtype == k_pages.dtype
@@ -564,8 +567,8 @@ def qkv_prepare(proj: torch.Tensor, q_out: torch.Tensor, heads: int, kv_heads: i
     _check(lib.de_qkv_prepare(_tag(proj.dtype), proj.data_ptr(), proj.stride(0), q_out.data_ptr(),
                               ctx.positions.data_ptr(), ctx.token_seq.data_ptr(),
                               ctx.token_slot.data_ptr(), ctx.seq_pos0.data_ptr(), _ptr(bias),
-                              *conv, *normed, *turned, *temp, *mixed, heads, kv_heads, key_dim,
-                              value_dim, k_pages.data_ptr(), v_pages.data_ptr(),
+                              *conv, *normed, *turned, *temp, *mixed, int(bool(keep_here)), heads,
+                              kv_heads, key_dim, value_dim, k_pages.data_ptr(), v_pages.data_ptr(),
                               block_table.data_ptr(), block_table.stride(0), k_pages.shape[2],
                               k_pages.shape[0], n, ctx.status.data_ptr(), _stream()),
            "qkv_prepare")

@@ -171,6 +171,7 @@ class SinkAttention(ProjectedMixer):
         if prep.has(name):
             return
         host = prep.host
+        prep.notes["sink_attention/single_tokens"] = int(host.seq_qlen.max()) == 1
         if int(host.seq_qlen.max()) == 1 and rk.chunk_decode_ok(self.dtype, self.heads,
                                                                self.kv_heads, self.dk, self.dv):
             # single tokens only: the kernel that takes a (sequence, kv head) a block, no items
@@ -206,13 +207,16 @@ class SinkAttention(ProjectedMixer):
                                  "earlier layer of the step that gives values of the same size")
             mix = ("take", first, self.lam)
         q = ctx.buffer("sink_attention.q", (n, H * dk))
+        # in a step of single tokens a slot is read by one block only, which then moves the
+        # slot's kept rows on itself
+        keep_here = state is not None and bool(ctx.notes.get("sink_attention/single_tokens"))
         rk.qkv_prepare(
             proj, q, H, G, dk, dv, pages.k_pages, pages.v_pages, pages.block_table, ctx,
             bias=self.bias, taps=self.conv, kept=(state.state, 0) if state is not None else None,
             norm=(self.norm, self.q_norm, self.k_norm, self.eps) if self.norm else None,
             rotation=(self.freq, self.magnitude, self.adjacent), temperature=self.temperature,
-            mix=mix)
-        if state is not None:
+            mix=mix, keep_here=keep_here)
+        if state is not None and not keep_here:
             rk.conv_keep(proj, state.state, 0, self.channels, self.taps, ctx)
         # the gate rides in the attention kernels' last step: the heads' results are multiplied
         # in float32 and rounded once
